@@ -1,0 +1,390 @@
+// Paged-attention decode over the device-resident KV pool.
+//
+// Entry b (one query position of one sequence) attends positions
+// start[b]..=pos[b]; logical block t / block_size is looked up once per block in
+// the entry's block-table row; a logical block past the mapped length scores
+// -inf (it is skipped: its K and V are never touched); an empty or fully masked
+// window gives zeros.  Query head h reads KV head h / kv_group.
+//
+// Fast path (head_dim 64 or 128, kv_group 1/2/4/8): one CTA per (kv head, entry,
+// KV split).  Each warp walks whole physical blocks; head_dim/8 lanes share a
+// token, each lane holding 8 dims of every query head of the group, so one
+// 2 x 128-bit load of K and of V per lane serves all kv_group query heads.
+// Softmax is online (running max / sum per head); warps and KV splits are merged
+// by log-sum-exp.  Generic path (any head_dim <= 512, any group, any block
+// size): one warp per (entry, query head).
+//
+// Replaces PagedAttention::run and for_each_block (reference
+// src/attention.rs:141-295), math::softmax_in_place (src/math.rs:405-426) and
+// BlockTable::get_physical_location (src/memory/block_table.rs:50-61).
+#include <math.h>
+
+#include <algorithm>
+
+#include "pi_common.cuh"
+
+namespace {
+
+constexpr int kAttnWarps = 4;
+
+struct AttnParams {
+  const float* q;
+  size_t q_stride;
+  float* out;
+  size_t out_stride;
+  const float* kv;
+  pi_kv_layout L;
+  int layer;
+  int H;
+  const int32_t* tables;
+  int max_blocks;
+  const int32_t* lens;
+  const int32_t* pos;
+  const int32_t* start;
+  int blocks_per_cta;
+  int nsplit;
+  float* part_ml;   // [B][H][nsplit][2]
+  float* part_acc;  // [B][H][nsplit][HD]
+  float scale;
+};
+
+__device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+
+// Merge (m, l, acc...) pairs: factor for a side with running max `m` once the joint max is `M`.
+__device__ __forceinline__ float lse_factor(float m, float M) { return m == -INFINITY ? 0.f : __expf(m - M); }
+
+template <int HD, int G>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const AttnParams p) {
+  constexpr int LPT = HD / 8;    // lanes per token
+  constexpr int TPW = 32 / LPT;  // tokens per warp step
+  __shared__ float s_acc[kAttnWarps][G][HD];
+  __shared__ float s_m[kAttnWarps][G], s_l[kAttnWarps][G];
+
+  pi_grid_dependency_wait();
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tg = lane / LPT, li = lane % LPT;
+  const int BS = p.L.block_size;
+  const int pos = p.pos[b], st = p.start[b], len = p.lens[b];
+  const int lb_first = st / BS, lb_last = pos / BS;
+  const int lb_begin = lb_first + split * p.blocks_per_cta;
+  const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);  // unmapped tail is masked
+
+  float qv[G][8];
+  const float* qb = p.q + (size_t)b * p.q_stride + (size_t)kvh * G * HD + li * 8;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float4 a = ldg_f4(qb + g * HD), c = ldg_f4(qb + g * HD + 4);
+    qv[g][0] = a.x; qv[g][1] = a.y; qv[g][2] = a.z; qv[g][3] = a.w;
+    qv[g][4] = c.x; qv[g][5] = c.y; qv[g][6] = c.z; qv[g][7] = c.w;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+  }
+
+  if (st <= pos) {
+    for (int lb = lb_begin + warp; lb < lb_end; lb += kAttnWarps) {
+      const int pb = p.tables[(size_t)b * p.max_blocks + lb];
+      const int t_lo = max(st - lb * BS, 0), t_hi = min(pos - lb * BS, BS - 1);
+      const float* Kt = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kvh, 0) + li * 8;
+      const float* Vt = Kt + (size_t)BS * HD;
+      for (int t0 = t_lo; t0 <= t_hi; t0 += TPW) {
+        const int t = t0 + tg;
+        const bool valid = t <= t_hi;
+        float kx[8], vx[8];
+        if (valid) {
+          const float4 k0 = ldg_f4(Kt + (size_t)t * HD), k1 = ldg_f4(Kt + (size_t)t * HD + 4);
+          const float4 v0 = ldg_f4(Vt + (size_t)t * HD), v1 = ldg_f4(Vt + (size_t)t * HD + 4);
+          kx[0] = k0.x; kx[1] = k0.y; kx[2] = k0.z; kx[3] = k0.w; kx[4] = k1.x; kx[5] = k1.y; kx[6] = k1.z; kx[7] = k1.w;
+          vx[0] = v0.x; vx[1] = v0.y; vx[2] = v0.z; vx[3] = v0.w; vx[4] = v1.x; vx[5] = v1.y; vx[6] = v1.z; vx[7] = v1.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) kx[i] = vx[i] = 0.f;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kx[i], d);
+#pragma unroll
+          for (int o = 1; o < LPT; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          const float s = valid ? d * p.scale : -INFINITY;
+          if (s > m[g]) {  // uniform across the LPT lanes of a token
+            const float corr = lse_factor(m[g], s);
+            l[g] *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] *= corr;
+            m[g] = s;
+          }
+          const float w = valid ? __expf(s - m[g]) : 0.f;
+          l[g] += w;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(w, vx[i], acc[g][i]);
+        }
+      }
+    }
+  }
+
+  // merge the token groups of the warp
+#pragma unroll
+  for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o), lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float M = fmaxf(m[g], mo);
+      const float fs = lse_factor(m[g], M), fo = lse_factor(mo, M);
+      l[g] = l[g] * fs + lo * fo;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+        acc[g][i] = acc[g][i] * fs + ao * fo;
+      }
+      m[g] = M;
+    }
+  }
+  if (tg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_acc[warp][g][li * 8 + i] = acc[g][i];
+      if (li == 0) {
+        s_m[warp][g] = m[g];
+        s_l[warp][g] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  pi_grid_launch_dependents();
+
+  // merge the warps; write the result or this split's partial
+  for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) {
+    const int g = idx / HD, d = idx - g * HD;
+    float M = s_m[0][g];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, s_m[w][g]);
+    float ls = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = lse_factor(s_m[w][g], M);
+      ls += s_l[w][g] * f;
+      a += s_acc[w][g][d] * f;
+    }
+    const int h = kvh * G + g;
+    if (p.nsplit == 1) {
+      p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = a * (1.0f / fmaxf(ls, 1e-12f));
+    } else {
+      const size_t slot = ((size_t)b * p.H + h) * p.nsplit + split;
+      p.part_acc[slot * HD + d] = a;
+      if (d == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = ls;
+      }
+    }
+  }
+}
+
+// grid (H, B), HD threads (rounded up to a warp): merge the KV splits.
+__global__ void attn_combine_kernel(const AttnParams p, int HD) {
+  pi_grid_dependency_wait();
+  const int h = blockIdx.x, b = blockIdx.y;
+  const size_t base = ((size_t)b * p.H + h) * p.nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s) M = fmaxf(M, p.part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float ls = 0.f, a = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float f = lse_factor(p.part_ml[(base + s) * 2], M);
+      ls += p.part_ml[(base + s) * 2 + 1] * f;
+      a += p.part_acc[(base + s) * HD + d] * f;
+    }
+    p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = a * (1.0f / fmaxf(ls, 1e-12f));
+  }
+}
+
+// Any shape: one warp per (query head, entry); lane owns dims lane, lane+32, ...
+constexpr int kGenericMaxPerLane = 16;
+__global__ void __launch_bounds__(32) attn_generic_kernel(const AttnParams p, int HD, int group) {
+  pi_grid_dependency_wait();
+  const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  const int kvh = h / group, BS = p.L.block_size;
+  const int pos = p.pos[b], st = p.start[b], len = p.lens[b];
+  float qv[kGenericMaxPerLane], acc[kGenericMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kGenericMaxPerLane; ++i) {
+    const int d = lane + 32 * i;
+    qv[i] = d < HD ? p.q[(size_t)b * p.q_stride + (size_t)h * HD + d] : 0.f;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int t = st; t <= pos; ++t) {
+    const int lb = t / BS;
+    if (lb >= len) break;  // everything further is unmapped as well
+    const int pb = p.tables[(size_t)b * p.max_blocks + lb];
+    const float* K = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kvh, 0) + (size_t)(t - lb * BS) * HD;
+    const float* V = K + (size_t)BS * HD;
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGenericMaxPerLane; ++i)
+      if (lane + 32 * i < HD) d = fmaf(qv[i], K[lane + 32 * i], d);
+    const float s = pi_warp_sum(d) * p.scale;
+    if (s > m) {
+      const float corr = m == -INFINITY ? 0.f : expf(m - s);
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < kGenericMaxPerLane; ++i) acc[i] *= corr;
+      m = s;
+    }
+    const float w = expf(s - m);
+    l += w;
+#pragma unroll
+    for (int i = 0; i < kGenericMaxPerLane; ++i)
+      if (lane + 32 * i < HD) acc[i] = fmaf(w, V[lane + 32 * i], acc[i]);
+  }
+  const float inv = 1.0f / fmaxf(l, 1e-12f);
+#pragma unroll
+  for (int i = 0; i < kGenericMaxPerLane; ++i)
+    if (lane + 32 * i < HD) p.out[(size_t)b * p.out_stride + (size_t)h * HD + lane + 32 * i] = acc[i] * inv;
+}
+
+template <typename K, typename... Args>
+cudaError_t launch_attn(pi_ctx* ctx, K kernel, dim3 grid, dim3 block, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <int HD>
+cudaError_t launch_fast(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p) {
+  switch (group) {
+    case 1: return launch_attn(ctx, attn_decode_kernel<HD, 1>, grid, dim3(kAttnWarps * 32), p);
+    case 2: return launch_attn(ctx, attn_decode_kernel<HD, 2>, grid, dim3(kAttnWarps * 32), p);
+    case 4: return launch_attn(ctx, attn_decode_kernel<HD, 4>, grid, dim3(kAttnWarps * 32), p);
+    default: return launch_attn(ctx, attn_decode_kernel<HD, 8>, grid, dim3(kAttnWarps * 32), p);
+  }
+}
+
+}  // namespace
+
+// Host block tables and per-entry metadata -> one device buffer, through pinned memory.
+pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
+                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size,
+                               pi_attn_batch* out) {
+  PI_REQUIRE(ctx, B > 0, "attention needs at least one entry");
+  PI_REQUIRE(ctx, max_blocks >= 0 && block_size > 0, "bad block table shape");
+  const int mb = std::max(max_blocks, 1);
+  const size_t n = (size_t)B * mb + 3 * (size_t)B;
+  PI_TRY(pi_reserve(ctx, &ctx->attn_tables, n * sizeof(int32_t)));
+  PI_TRY(pi_reserve_pinned(ctx, n * sizeof(int32_t)));
+  int32_t* h = static_cast<int32_t*>(ctx->pinned);
+  int32_t* h_lens = h + (size_t)B * mb;
+  int32_t* h_pos = h_lens + B;
+  int32_t* h_start = h_pos + B;
+  long total = 0;
+  int widest = 0;
+  for (int b = 0; b < B; ++b) {
+    const int len = lens_host[b];
+    PI_REQUIRE(ctx, len >= 0 && len <= max_blocks, "entry %d: table length %d outside [0, %d]", b, len, max_blocks);
+    PI_REQUIRE(ctx, pos_host[b] >= 0 && start_host[b] >= 0, "entry %d: negative position", b);
+    for (int i = 0; i < mb; ++i) h[(size_t)b * mb + i] = (i < len) ? tables_host[(size_t)b * max_blocks + i] : -1;
+    h_lens[b] = len;
+    h_pos[b] = pos_host[b];
+    h_start[b] = start_host[b];
+    if (start_host[b] <= pos_host[b]) {
+      const int nb = pos_host[b] / block_size - start_host[b] / block_size + 1;
+      total += nb;
+      widest = std::max(widest, nb);
+    }
+  }
+  int32_t* d = static_cast<int32_t*>(ctx->attn_tables.ptr);
+  PI_CUDA(ctx, cudaMemcpyAsync(d, h, n * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  out->tables = d;
+  out->max_blocks = mb;
+  out->lens = d + (size_t)B * mb;
+  out->pos = out->lens + B;
+  out->start = out->pos + B;
+  out->B = B;
+  out->max_window_blocks = widest;
+  out->total_window_blocks = total;
+  return PI_OK;
+}
+
+pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
+                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch) {
+  const pi_kv_layout& L = pool->L;
+  PI_REQUIRE(ctx, layer >= 0 && layer < L.num_layers, "layer %d outside the pool's %d layers", layer, L.num_layers);
+  PI_REQUIRE(ctx, L.num_kv_heads > 0 && num_heads % L.num_kv_heads == 0 && num_heads > 0,
+             "num_attention_heads (%d) must be a multiple of num_key_value_heads (%d)", num_heads, L.num_kv_heads);
+  const int group = num_heads / L.num_kv_heads, HD = L.head_dim;
+  AttnParams p;
+  p.q = q;
+  p.q_stride = q_stride;
+  p.out = out;
+  p.out_stride = out_stride;
+  p.kv = pool->data;
+  p.L = L;
+  p.layer = layer;
+  p.H = num_heads;
+  p.tables = batch.tables;
+  p.max_blocks = batch.max_blocks;
+  p.lens = batch.lens;
+  p.pos = batch.pos;
+  p.start = batch.start;
+  p.scale = 1.0f / sqrtf((float)HD);
+  p.nsplit = 1;
+  p.blocks_per_cta = std::max(batch.max_window_blocks, 1);
+  p.part_ml = nullptr;
+  p.part_acc = nullptr;
+
+  const bool fast = (HD == 64 || HD == 128) && (group == 1 || group == 2 || group == 4 || group == 8) &&
+                    ((uintptr_t)q % 16 == 0) && (q_stride % 4 == 0);
+  cudaError_t e;
+  if (!fast) {
+    PI_REQUIRE(ctx, HD <= 32 * kGenericMaxPerLane, "head_dim %d is not supported (max %d)", HD, 32 * kGenericMaxPerLane);
+    e = launch_attn(ctx, attn_generic_kernel, dim3(num_heads, batch.B), dim3(32), p, HD, group);
+    if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    ctx->launches++;
+    return PI_OK;
+  }
+
+  // Split the KV axis so that about four CTAs per SM stream the pool.
+  const long pairs_blocks = batch.total_window_blocks * L.num_kv_heads;
+  const long target_ctas = (long)ctx->sm_count * 4;
+  int bpc = (int)((pairs_blocks + target_ctas - 1) / target_ctas);
+  bpc = std::max(bpc, kAttnWarps);
+  bpc = (bpc + kAttnWarps - 1) / kAttnWarps * kAttnWarps;
+  int nsplit = (std::max(batch.max_window_blocks, 1) + bpc - 1) / bpc;
+  if (nsplit > 64) {
+    nsplit = 64;
+    bpc = (batch.max_window_blocks + nsplit - 1) / nsplit;
+  }
+  p.blocks_per_cta = bpc;
+  p.nsplit = nsplit;
+  if (nsplit > 1) {
+    const size_t slots = (size_t)batch.B * num_heads * nsplit;
+    PI_TRY(pi_reserve(ctx, &ctx->attn_partial, slots * (HD + 2) * sizeof(float)));
+    p.part_acc = static_cast<float*>(ctx->attn_partial.ptr);
+    p.part_ml = p.part_acc + slots * HD;
+  }
+  const dim3 grid(L.num_kv_heads, batch.B, nsplit);
+  e = HD == 64 ? launch_fast<64>(ctx, group, grid, p) : launch_fast<128>(ctx, group, grid, p);
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
+  if (nsplit > 1) {
+    e = launch_attn(ctx, attn_combine_kernel, dim3(num_heads, batch.B), dim3(HD), p, HD);
+    if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention combine launch failed: %s", cudaGetErrorString(e));
+    ctx->launches++;
+  }
+  return PI_OK;
+}

@@ -1,0 +1,212 @@
+// Internal declarations shared by the translation units of libpaged_infer_cuda.so.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/paged_infer_cuda.h"
+
+#define PI_WARP 32
+
+// ---- error plumbing -----------------------------------------------------------
+pi_status pi_fail(pi_ctx* ctx, pi_status code, const char* fmt, ...);
+void pi_set_global_error(const char* msg);
+
+#define PI_CUDA(ctx, expr)                                                                        \
+  do {                                                                                            \
+    cudaError_t _e = (expr);                                                                      \
+    if (_e != cudaSuccess)                                                                        \
+      return pi_fail((ctx), _e == cudaErrorMemoryAllocation ? PI_ERR_OOM : PI_ERR_CUDA,           \
+                     "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+  } while (0)
+
+#define PI_CHECK_LAUNCH(ctx)                                                                           \
+  do {                                                                                                 \
+    cudaError_t _e = cudaGetLastError();                                                               \
+    if (_e != cudaSuccess)                                                                             \
+      return pi_fail((ctx), PI_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e),   \
+                     __FILE__, __LINE__);                                                              \
+    (ctx)->launches++;                                                                                 \
+  } while (0)
+
+#define PI_REQUIRE(ctx, cond, ...)                                     \
+  do {                                                                 \
+    if (!(cond)) return pi_fail((ctx), PI_ERR_INVALID_ARG, __VA_ARGS__); \
+  } while (0)
+
+#define PI_TRY(expr)               \
+  do {                             \
+    pi_status _s = (expr);         \
+    if (_s != PI_OK) return _s;    \
+  } while (0)
+
+// ---- context ------------------------------------------------------------------
+// A growable device buffer owned by the context (scratch that outlives a call).
+struct pi_buffer {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+
+struct pi_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 148;
+  size_t smem_optin = 0;
+  std::string err;
+  uint64_t launches = 0;
+  int* dev_err = nullptr;   // device word set by a kernel whose bounded wait ran out
+
+  // tensor parallelism
+  int rank = 0, tp = 1;
+  void* nccl_comm = nullptr;  // ncclComm_t
+
+  // options
+  bool opt_tensor_gemm = true;
+  bool opt_graph = true;
+  bool opt_pdl = true;
+  int opt_gemv_max_m = 4;
+
+  // scratch
+  pi_buffer staging_in, staging_out;   // device copies of host arguments / results
+  pi_buffer attn_tables, attn_meta;    // block tables + per-entry (len, pos, start)
+  pi_buffer attn_partial;              // split-KV partial (m, l, acc)
+  pi_buffer gemm_act;                  // fp16 hi/lo activation planes for the tensor GEMM
+  pi_buffer gemm_partial;              // split-K partial sums
+  void* pinned = nullptr;              // pinned host staging
+  size_t pinned_bytes = 0;
+};
+
+pi_status pi_reserve(pi_ctx* ctx, pi_buffer* buf, size_t bytes);
+pi_status pi_reserve_pinned(pi_ctx* ctx, size_t bytes);
+
+// ---- projections ----------------------------------------------------------------
+struct pi_linear {
+  int kind = PI_INT8;          // PI_F32 / PI_INT8 / PI_BF16
+  pi_split split = PI_SPLIT_NONE;
+  size_t full_rows = 0, full_cols = 0;
+  size_t rows = 0, cols = 0;   // local shard
+  size_t ld = 0;               // row stride in elements (rows start 16-byte aligned, zero padded)
+  void* w = nullptr;           // [rows][ld]
+  float* scales = nullptr;     // [rows] (int8 only)
+  bool owns = true;
+};
+
+enum pi_epilogue {
+  PI_EPI_STORE = 0,     // out[m][r] = v
+  PI_EPI_ADD = 1,       // out[m][r] += v           (residual add)
+  PI_EPI_SWIGLU = 2     // rows interleaved gate/up: out[m][r/2] = silu(v[2i]) * v[2i+1]
+};
+
+struct pi_linear_args {
+  const float* x = nullptr;   // [M][x_stride]
+  size_t x_stride = 0;
+  float* out = nullptr;       // [M][out_stride]
+  size_t out_stride = 0;
+  int M = 1;
+  pi_epilogue epi = PI_EPI_STORE;
+  const float* norm_weight = nullptr;  // fused RMSNorm prologue when non-null
+  float norm_eps = 0.f;
+};
+
+// CUDA-core dequant GEMV/GEMM (any shape, any M).
+pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+// tcgen05 tensor-core GEMM for int8 weights (returns PI_ERR_UNSUPPORTED when the shape does not fit).
+pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+bool pi_gemm_tc_supported(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+// Dispatch between the two.
+pi_status pi_linear_forward(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+
+pi_status pi_linear_alloc(pi_ctx* ctx, int kind, size_t full_rows, size_t full_cols, pi_split split, pi_linear** out);
+// Copy a [rows x cols] host or device matrix (row stride src_ld elements) into the padded device layout.
+pi_status pi_linear_fill(pi_ctx* ctx, pi_linear* lin, const void* src, size_t src_ld, bool src_on_device);
+pi_status pi_launch_quantize(pi_ctx* ctx, const float* w_dev, size_t w_ld, size_t rows, size_t cols, int8_t* q_dev,
+                             size_t q_ld, float* scales_dev);
+
+// ---- KV pool ----------------------------------------------------------------------
+// Device layout: [layer][block][kv_head][k|v][token][head_dim] f32, so one
+// (block, kv_head) K tile is block_size*head_dim contiguous floats with its V
+// tile right behind it, and one block of one layer is still one contiguous span.
+struct pi_kv_pool {
+  pi_kv_layout L;
+  float* data = nullptr;
+  size_t floats = 0;
+  __host__ __device__ size_t block_stride() const { return (size_t)L.block_size * L.num_kv_heads * 2 * L.head_dim; }
+};
+
+__host__ __device__ inline size_t pi_kv_tile_offset(const pi_kv_layout& L, int layer, int block, int kv_head, int is_v) {
+  return ((((size_t)layer * L.num_blocks + block) * L.num_kv_heads + kv_head) * 2 + is_v) * ((size_t)L.block_size * L.head_dim);
+}
+
+// ---- attention ----------------------------------------------------------------------
+struct pi_attn_batch {
+  const int32_t* tables = nullptr;  // device [B][max_blocks]
+  int max_blocks = 0;
+  const int32_t* lens = nullptr;    // device [B]
+  const int32_t* pos = nullptr;     // device [B]
+  const int32_t* start = nullptr;   // device [B]
+  int B = 0;
+  int max_window_blocks = 0;        // host-side bound on blocks any window touches
+  long total_window_blocks = 0;     // host-side sum
+};
+pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
+                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size,
+                               pi_attn_batch* out);
+pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
+                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
+
+// ---- glue ----------------------------------------------------------------------------
+pi_status pi_launch_embed(pi_ctx* ctx, const uint16_t* table_bf16, int vocab, int hidden, const uint32_t* tokens_dev,
+                          int B, float* x);
+pi_status pi_launch_rms_norm(pi_ctx* ctx, float* x, size_t stride, const float* weight, int rows, int n, float eps);
+// Rotate q (in place) and k, then scatter k and v into the pool. qkv is [B][qkv_stride] = [q | k | v].
+pi_status pi_launch_rope_kv_write(pi_ctx* ctx, float* qkv, size_t qkv_stride, int num_heads, int num_kv_heads,
+                                  int head_dim, const float* rope_cos, const float* rope_sin, int style,
+                                  pi_kv_pool* pool, int layer, const pi_attn_batch& batch);
+pi_status pi_launch_rope(pi_ctx* ctx, float* x, size_t stride, int heads, int head_dim, const int32_t* pos_dev,
+                         const float* rope_cos, const float* rope_sin, int style, int rows);
+pi_status pi_launch_swiglu(pi_ctx* ctx, float* gate, const float* up, size_t n);
+pi_status pi_launch_add(pi_ctx* ctx, float* x, const float* y, size_t n);
+pi_status pi_launch_argmax(pi_ctx* ctx, const float* logits, size_t stride, int rows, int n, uint32_t* out);
+pi_status pi_launch_copy_block(pi_ctx* ctx, pi_kv_pool* pool, int src, int dst);
+pi_status pi_launch_kv_relayout(pi_ctx* ctx, const pi_kv_pool* pool, float* ref_layout, bool to_reference);
+// N(0, std) from a counter-based generator keyed by (seed, stream id); element 2i and 2i+1 come from
+// counter pair_offset + i, so any even-aligned slice of a tensor reproduces the whole tensor's values.
+pi_status pi_launch_fill_normal(pi_ctx* ctx, float* out, size_t n, uint64_t seed, uint64_t stream_id,
+                                uint64_t pair_offset, float std);
+pi_status pi_launch_f32_to_bf16(pi_ctx* ctx, const float* in, uint16_t* out, size_t n);
+pi_status pi_launch_bf16_to_f32(pi_ctx* ctx, const uint16_t* in, size_t in_ld, float* out, size_t out_ld, size_t rows, size_t cols);
+
+// Host rotary table exactly as the reference builds it (f32 powf/sinf/cosf of the host libm).
+void pi_host_rope_table(int pos, int head_dim, float theta, float* cos_out, float* sin_out);
+
+// ---- tensor parallel -------------------------------------------------------------------
+pi_status pi_tp_init(pi_ctx* ctx, const void* unique_id);
+void pi_tp_destroy(pi_ctx* ctx);
+pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n);
+pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t bytes_per_rank);
+
+// ---- device helpers ----------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float pi_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float pi_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float pi_bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+// Programmatic dependent launch: wait for the producer grid's memory, and allow
+// the consumer grid to start its prologue.
+__device__ __forceinline__ void pi_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pi_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif

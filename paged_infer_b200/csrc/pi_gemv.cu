@@ -1,0 +1,425 @@
+// Dequantising GEMV / small-batch GEMM on CUDA cores, and the row quantiser.
+//
+// y[m][r] = scale[r] * sum_k W[r][k] * x[m][k] with W int8 (or bf16 / f32 with
+// scale 1), x f32, f32 accumulation.  This is the decode-sized path: every
+// weight byte is read from HBM exactly once per launch with 128-bit loads, the
+// activations are staged into shared memory once per CTA by a bulk async copy
+// (TMA, cp.async.bulk) and read back conflict-free, each warp owns two output
+// rows and reduces with shuffles.  Optional fusions: an RMSNorm prologue on x,
+// and residual-add or SwiGLU epilogues.
+//
+// Replaces math::matvec_i8_weight_parallel / matmat_i8_weight_parallel and the
+// f32 twins (reference src/math.rs:93-275, :473-512) and math::quantize_rows_i8
+// (:456-469).
+#include "pi_common.cuh"
+
+namespace {
+
+constexpr int kRows = 2;       // output rows per warp
+constexpr int kMaxMB = 4;      // activation rows per CTA pass
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ int4 ld_stream_16(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// 16 bytes of weights -> EPL floats.
+template <typename WT>
+struct Widen;
+template <>
+struct Widen<int8_t> {
+  static constexpr int EPL = 16;
+  // int8 -> f32 without the quarter-rate I2F: flip the sign bit so the byte is
+  // b+128 in [0,255], drop it into the mantissa of 2^23, subtract 2^23+128.
+  __device__ static __forceinline__ void run(const int4& v, float* f) {
+    const uint32_t w[4] = {(uint32_t)v.x ^ 0x80808080u, (uint32_t)v.y ^ 0x80808080u, (uint32_t)v.z ^ 0x80808080u,
+                           (uint32_t)v.w ^ 0x80808080u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[4 * i + 0] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.0f;
+      f[4 * i + 1] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.0f;
+      f[4 * i + 2] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.0f;
+      f[4 * i + 3] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)) - 8388736.0f;
+    }
+  }
+};
+template <>
+struct Widen<uint16_t> {  // bf16 bits
+  static constexpr int EPL = 8;
+  __device__ static __forceinline__ void run(const int4& v, float* f) {
+    const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i + 0] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+};
+template <>
+struct Widen<float> {
+  static constexpr int EPL = 4;
+  __device__ static __forceinline__ void run(const int4& v, float* f) {
+    f[0] = __int_as_float(v.x);
+    f[1] = __int_as_float(v.y);
+    f[2] = __int_as_float(v.z);
+    f[3] = __int_as_float(v.w);
+  }
+};
+
+struct GemvParams {
+  const void* W;
+  const float* scales;
+  const float* x;
+  float* out;
+  const float* norm_weight;
+  size_t ld, x_stride, out_stride;
+  int N, K, M;
+  float eps;
+  int use_tma;
+  int* err_flag;
+};
+
+// A lane reads U = EPL/4 consecutive 16-byte units of x per step.  Stored
+// linearly that is a U-way bank conflict for 128-bit shared loads, so unit j of
+// lane-group g lives at slot j ^ s(g): every quarter warp then touches eight
+// distinct 16-byte bank groups.
+template <int U>
+__device__ __forceinline__ int unit_swizzle(int group) {
+  if (U == 4) return (group >> 1) & 3;
+  if (U == 2) return (group >> 2) & 1;
+  return 0;
+}
+
+template <typename WT, int MB, int EPI, bool NORM>
+__global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
+  constexpr int EPL = Widen<WT>::EPL;
+  constexpr int U = EPL / 4;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  float* xs = reinterpret_cast<float*>(smem_raw);  // [MB][ld]
+  __shared__ __align__(8) unsigned long long mbar;
+  __shared__ float red[MB][8];
+  __shared__ float inv_norm[MB];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int ld = (int)p.ld, K = p.K;
+  const int m0 = blockIdx.y * MB;
+  const int mcount = min(MB, p.M - m0);
+
+  // Weight rows of this warp; the first 16-byte chunks are requested before the
+  // activations are waited for, since they do not depend on the producer kernel.
+  const int row0 = (blockIdx.x * nwarps + warp) * kRows;
+  const unsigned char* wrow[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int row = min(row0 + r, p.N - 1);
+    wrow[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * ld * sizeof(WT);
+  }
+  int k0 = lane * EPL;
+  int4 wv[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) wv[r] = (k0 < ld) ? ld_stream_16(wrow[r] + (size_t)k0 * sizeof(WT)) : make_int4(0, 0, 0, 0);
+
+  pi_grid_dependency_wait();
+
+  // ---- stage x[m0 .. m0+mcount) into shared memory --------------------------
+  bool landed = false;
+  if (p.use_tma) {
+    if (tid == 0) {
+      const uint32_t bar = smem_u32(&mbar);
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      const uint32_t bytes = (uint32_t)(mcount * K * sizeof(float));
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      for (int m = 0; m < mcount; ++m) {
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                smem_u32(xs + (size_t)m * ld)),
+            "l"(p.x + (size_t)(m0 + m) * p.x_stride), "r"((uint32_t)(K * sizeof(float))), "r"(bar)
+            : "memory");
+      }
+    }
+    // zero the padding and the unused batch rows (disjoint from the copy's bytes)
+    for (int m = 0; m < MB; ++m) {
+      const int from = (m < mcount) ? K : 0;
+      for (int k = from + tid; k < ld; k += blockDim.x) xs[(size_t)m * ld + k] = 0.f;
+    }
+    __syncthreads();  // barrier initialised before anyone polls it
+    const uint32_t bar = smem_u32(&mbar);
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < kSpinLimit && !done; ++spin) {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done)
+          : "r"(bar), "r"(0u)
+          : "memory");
+    }
+    landed = __syncthreads_and((int)done) != 0;
+    if (!landed && tid == 0 && p.err_flag) atomicExch(p.err_flag, 1);  // bulk copy never completed: reload below
+  }
+  if (!landed) {
+    for (int m = 0; m < MB; ++m) {
+      const float* src = p.x + (size_t)(m0 + m) * p.x_stride;
+      for (int k = tid; k < ld; k += blockDim.x) xs[(size_t)m * ld + k] = (m < mcount && k < K) ? src[k] : 0.f;
+    }
+    __syncthreads();
+  }
+
+  // ---- optional RMSNorm: mean of squares per activation row -----------------
+  if (NORM) {
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      float ss = 0.f;
+      for (int k = tid; k < K; k += blockDim.x) {
+        const float v = xs[(size_t)m * ld + k];
+        ss = fmaf(v, v, ss);
+      }
+      ss = pi_warp_sum(ss);
+      if (lane == 0) red[m][warp] = ss;
+    }
+    __syncthreads();
+    if (tid < MB) {
+      float ss = 0.f;
+      for (int w = 0; w < nwarps; ++w) ss += red[tid][w];
+      inv_norm[tid] = 1.0f / sqrtf(ss / (float)K + p.eps);
+    }
+    __syncthreads();
+  }
+  // ---- in-place pass per EPL-float group: scale by the norm and swizzle units -
+  {
+    const int groups = ld / EPL;
+    for (int idx = tid; idx < groups * MB; idx += blockDim.x) {
+      const int m = idx / groups, g = idx - m * groups;
+      float4* base = reinterpret_cast<float4*>(xs + (size_t)m * ld + (size_t)g * EPL);
+      float4 u[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) u[j] = base[j];
+      if (NORM) {
+        const float inv = inv_norm[m];
+        const float4* nw = reinterpret_cast<const float4*>(p.norm_weight + (size_t)g * EPL);
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          const int kk = g * EPL + 4 * j;
+          float4 w4 = (kk + 3 < K) ? nw[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+          if (kk < K && kk + 3 >= K) {  // ragged tail of the norm weight
+            w4.x = p.norm_weight[kk];
+            w4.y = kk + 1 < K ? p.norm_weight[kk + 1] : 0.f;
+            w4.z = kk + 2 < K ? p.norm_weight[kk + 2] : 0.f;
+            w4.w = 0.f;
+          }
+          u[j].x = u[j].x * inv * w4.x;
+          u[j].y = u[j].y * inv * w4.y;
+          u[j].z = u[j].z * inv * w4.z;
+          u[j].w = u[j].w * inv * w4.w;
+        }
+      }
+      const int s = unit_swizzle<U>(g & 31);
+#pragma unroll
+      for (int j = 0; j < U; ++j) base[j ^ s] = u[j];
+    }
+    __syncthreads();
+  }
+  pi_grid_launch_dependents();
+
+  // ---- stream the weight rows -------------------------------------------------
+  float acc[kRows][MB];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+
+  const int s = unit_swizzle<U>(lane);
+  for (; k0 < ld; k0 += 32 * EPL) {
+    const int kn = k0 + 32 * EPL;
+    int4 wn[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) wn[r] = (kn < ld) ? ld_stream_16(wrow[r] + (size_t)kn * sizeof(WT)) : make_int4(0, 0, 0, 0);
+
+    float wf[kRows][EPL];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) Widen<WT>::run(wv[r], wf[r]);
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      const float4* xb = reinterpret_cast<const float4*>(xs + (size_t)m * ld + k0);
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const float4 xv = xb[j ^ s];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+          acc[r][m] = fmaf(wf[r][4 * j + 0], xv.x, acc[r][m]);
+          acc[r][m] = fmaf(wf[r][4 * j + 1], xv.y, acc[r][m]);
+          acc[r][m] = fmaf(wf[r][4 * j + 2], xv.z, acc[r][m]);
+          acc[r][m] = fmaf(wf[r][4 * j + 3], xv.w, acc[r][m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) wv[r] = wn[r];
+  }
+
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[r][m] = pi_warp_sum(acc[r][m]);
+
+  // ---- epilogue ------------------------------------------------------------------
+  if (row0 >= p.N) return;
+  float sc[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) sc[r] = (p.scales && row0 + r < p.N) ? p.scales[row0 + r] : 1.0f;
+  if (EPI == PI_EPI_SWIGLU) {
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (lane == m && m < mcount) {
+        const float g = acc[0][m] * sc[0], u = acc[1][m] * sc[1];
+        p.out[(size_t)(m0 + m) * p.out_stride + (row0 >> 1)] = (g / (1.0f + expf(-g))) * u;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        if (lane == r * MB + m && m < mcount && row0 + r < p.N) {
+          float* o = p.out + (size_t)(m0 + m) * p.out_stride + row0 + r;
+          const float v = acc[r][m] * sc[r];
+          *o = (EPI == PI_EPI_ADD) ? (*o + v) : v;
+        }
+      }
+  }
+}
+
+template <typename WT, int MB>
+cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, dim3 grid, int threads, size_t smem,
+                          bool pdl) {
+  void (*k)(const GemvParams) = nullptr;
+#define PI_PICK(E, Nrm) k = gemv_kernel<WT, MB, E, Nrm>
+  if (epi == PI_EPI_STORE) {
+    if (norm) PI_PICK(PI_EPI_STORE, true); else PI_PICK(PI_EPI_STORE, false);
+  } else if (epi == PI_EPI_ADD) {
+    if (norm) PI_PICK(PI_EPI_ADD, true); else PI_PICK(PI_EPI_ADD, false);
+  } else {
+    if (norm) PI_PICK(PI_EPI_SWIGLU, true); else PI_PICK(PI_EPI_SWIGLU, false);
+  }
+#undef PI_PICK
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, k, p);
+}
+
+template <typename WT>
+cudaError_t launch_gemv_w(pi_ctx* ctx, const GemvParams& p, int mb, int epi, bool norm, dim3 grid, int threads,
+                          size_t smem, bool pdl) {
+  switch (mb) {
+    case 1: return launch_gemv_t<WT, 1>(ctx, p, epi, norm, grid, threads, smem, pdl);
+    case 2: return launch_gemv_t<WT, 2>(ctx, p, epi, norm, grid, threads, smem, pdl);
+    default: return launch_gemv_t<WT, 4>(ctx, p, epi, norm, grid, threads, smem, pdl);
+  }
+}
+
+// ---- quantiser ---------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ w, size_t w_ld, int cols,
+                                                            int8_t* __restrict__ q, size_t q_ld,
+                                                            float* __restrict__ scales) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  const size_t row = blockIdx.x;
+  const float* src = w + row * w_ld;
+  float m = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, fabsf(src[c]));  // fmaxf drops NaN like f32::max
+  m = pi_warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mm = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) mm = fmaxf(mm, red[i]);
+    const float scale = mm > 0.f ? __fdiv_rn(mm, 127.0f) : 1.0f;
+    s_scale = scale;
+    scales[row] = scale;
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  int8_t* dst = q + row * q_ld;
+  for (int c = threadIdx.x; c < (int)q_ld; c += blockDim.x) {
+    int8_t code = 0;
+    if (c < cols) {
+      float v = roundf(__fdiv_rn(src[c], scale));  // half away from zero, true division
+      v = fminf(fmaxf(v, -127.0f), 127.0f);        // NaN survives to the cast below, as in Rust's clamp
+      code = (v != v) ? (int8_t)0 : (int8_t)(int)v;
+    }
+    dst[c] = code;  // padding columns are zero
+  }
+}
+
+}  // namespace
+
+pi_status pi_launch_quantize(pi_ctx* ctx, const float* w_dev, size_t w_ld, size_t rows, size_t cols, int8_t* q_dev,
+                             size_t q_ld, float* scales_dev) {
+  if (rows == 0) return PI_OK;
+  quantize_rows_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(w_dev, w_ld, (int)cols, q_dev, q_ld, scales_dev);
+  PI_CHECK_LAUNCH(ctx);
+  return PI_OK;
+}
+
+pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
+  PI_REQUIRE(ctx, a.M >= 1, "projection batch must be at least 1");
+  PI_REQUIRE(ctx, a.epi != PI_EPI_SWIGLU || lin->rows % 2 == 0, "SwiGLU epilogue needs interleaved gate/up rows");
+  if (lin->rows == 0) return PI_OK;
+  const size_t esz = lin->kind == PI_INT8 ? 1 : lin->kind == PI_BF16 ? 2 : 4;
+  (void)esz;
+  int mb = a.M >= 4 ? 4 : a.M >= 2 ? 2 : 1;
+  while (mb > 1 && (size_t)mb * lin->ld * sizeof(float) > ctx->smem_optin - 2048) mb >>= 1;
+  const size_t smem = (size_t)mb * lin->ld * sizeof(float);
+  PI_REQUIRE(ctx, smem <= ctx->smem_optin - 2048, "projection input of %zu columns does not fit shared memory", lin->cols);
+
+  // Enough CTAs to cover the SMs a few times over; wide CTAs only for tall matrices.
+  int warps = 8;
+  while (warps > 2 && (lin->rows + (size_t)warps * kRows - 1) / ((size_t)warps * kRows) < (size_t)ctx->sm_count * 2) warps >>= 1;
+  dim3 grid((unsigned)((lin->rows + (size_t)warps * kRows - 1) / ((size_t)warps * kRows)), (unsigned)((a.M + mb - 1) / mb));
+
+  GemvParams p;
+  p.W = lin->w;
+  p.scales = lin->kind == PI_INT8 ? lin->scales : nullptr;
+  p.x = a.x;
+  p.out = a.out;
+  p.norm_weight = a.norm_weight;
+  p.ld = lin->ld;
+  p.x_stride = a.x_stride;
+  p.out_stride = a.out_stride;
+  p.N = (int)lin->rows;
+  p.K = (int)lin->cols;
+  p.M = a.M;
+  p.eps = a.norm_eps;
+  p.err_flag = ctx->dev_err;
+  p.use_tma = ((lin->cols * sizeof(float)) % 16 == 0) && ((uintptr_t)a.x % 16 == 0) &&
+              ((a.x_stride * sizeof(float)) % 16 == 0) && ((size_t)mb * lin->cols * sizeof(float) < (1u << 20));
+  const bool norm = a.norm_weight != nullptr;
+  cudaError_t e;
+  if (lin->kind == PI_INT8)
+    e = launch_gemv_w<int8_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+  else if (lin->kind == PI_BF16)
+    e = launch_gemv_w<uint16_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+  else
+    e = launch_gemv_w<float>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
+  return PI_OK;
+}

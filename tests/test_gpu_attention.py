@@ -1,0 +1,159 @@
+"""Paged attention on the GPU against the oracle's PagedAttention::run and the
+naive per-head reference, restating tests/attention_tests.rs, plus the KV pool
+calls.  Tolerance 1e-5 relative to max(|expected|, 1): the GPU keeps an online
+softmax and a different summation order, the arithmetic is otherwise the same."""
+import numpy as np
+import pytest
+
+from helpers import AttnCase, normal_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from paged_infer_b200 import api
+    c = api.Context(0)
+    yield c
+    c.close()
+
+
+def gpu_run(ctx, case, q, tables, positions, starts, layer=0):
+    from paged_infer_b200 import api
+    L = api.KvLayout(case.num_layers, case.total_blocks, case.block_size, case.num_kv_heads, case.head_dim)
+    kv = api.KvCache(ctx, L)
+    kv.upload(case.kv_cache)
+    entries = [api.AttnEntry(api.BlockTable(t), p, start=s) for t, p, s in zip(tables, positions, starts)]
+    return api.PagedAttention(L, case.num_heads).run(q, kv, entries, layer)
+
+
+def cpu_run(oracle, case, q, tables, positions, starts, layer=0):
+    L = oracle.kv_layout(case.num_layers, case.total_blocks, case.block_size, case.num_kv_heads, case.head_dim)
+    return oracle.paged_attention(q, case.kv_cache, L, case.num_heads, tables, positions, starts, layer=layer)
+
+
+def close(got, want, tol=1e-5):
+    err = np.abs(got - want) / np.maximum(np.abs(want), 1.0)
+    assert err.max() < tol, err.max()
+
+
+def test_reference_head_shapes_ragged_batches(ctx, oracle):  # attention_tests.rs:168-194
+    for H, KH in [(8, 1), (8, 2), (8, 4), (8, 8), (6, 3), (12, 4)]:
+        for batch in (1, 3):
+            case = AttnCase(H, KH, 4, 8, batch, 5, 5)
+            pos = [39 - b * 9 for b in range(batch)]
+            st = [0] * batch
+            got = gpu_run(ctx, case, case.q, case.tables, pos, st)
+            close(got, cpu_run(oracle, case, case.q, case.tables, pos, st))
+            close(got, case.naive(case.q, case.tables, pos, st))
+
+
+def test_windows_and_block_boundaries(ctx, oracle):  # attention_tests.rs:197-225, :256-276
+    case = AttnCase(8, 2, 4, 8, 1, 6, 6)
+    for pos in range(0, 48, 3):
+        for window in (None, 1, 2, 7, 8, 9, 16, 33):
+            st = case.starts([pos], window)
+            close(gpu_run(ctx, case, case.q, case.tables, [pos], st), cpu_run(oracle, case, case.q, case.tables, [pos], st))
+    case = AttnCase(8, 4, 4, 16, 1, 4, 4)
+    for pos in (0, 1, 15, 16, 17, 31, 47):
+        for window in (1, 2, 3):
+            st = case.starts([pos], window)
+            close(gpu_run(ctx, case, case.q, case.tables, [pos], st), cpu_run(oracle, case, case.q, case.tables, [pos], st))
+
+
+def test_unmapped_positions_are_masked_not_read(ctx, oracle):  # attention_tests.rs:228-253
+    case = AttnCase(8, 2, 4, 8, 1, 6, 2)
+    full = gpu_run(ctx, case, case.q, case.tables, [40], [0])
+    trunc = gpu_run(ctx, case, case.q, case.tables, [15], [0])
+    assert np.array_equal(full, trunc) and np.all(np.isfinite(full))
+    close(full, cpu_run(oracle, case, case.q, case.tables, [40], [0]))
+    # nothing mapped at all, and a window that lies wholly in the unmapped tail: zeros, not NaN
+    assert np.all(gpu_run(ctx, case, case.q, [[]], [5], [0]) == 0.0)
+    assert np.all(gpu_run(ctx, case, case.q, case.tables, [40], [30]) == 0.0)
+
+
+def test_shared_table_entries_stay_independent(ctx, oracle):  # attention_tests.rs:279-322
+    case = AttnCase(8, 2, 4, 8, 3, 5, 5)
+    positions = [7, 19, 33]
+    shared = [case.tables[0]] * 3
+    got = gpu_run(ctx, case, case.q, shared, positions, [0, 0, 0])
+    close(got, cpu_run(oracle, case, case.q, shared, positions, [0, 0, 0]))
+    per = 8 * 4
+    for i, p in enumerate(positions):
+        solo = gpu_run(ctx, case, case.q[i * per:(i + 1) * per], [case.tables[0]], [p], [0])
+        assert np.array_equal(got[i], solo[0])
+
+
+def test_zero_width_window_is_zeros(ctx):  # attention_tests.rs:325-341
+    case = AttnCase(8, 2, 4, 8, 1, 4, 4)
+    assert np.all(gpu_run(ctx, case, case.q, case.tables, [20], [21]) == 0.0)
+
+
+@pytest.mark.parametrize("hd,H,KH,bs", [(64, 32, 4, 16), (128, 32, 8, 16), (128, 8, 1, 16), (64, 4, 4, 16), (64, 8, 4, 8),
+                                        (128, 4, 2, 32), (24, 4, 2, 16), (64, 12, 4, 16)])
+def test_model_head_shapes_random_kv(ctx, oracle, hd, H, KH, bs):
+    """TinyLlama / Llama-3 / Llama-2-70B head geometry (fast path) and the fixture's head_dim 24 (generic path)."""
+    rng = np.random.default_rng(hd + H)
+    batch, blocks_per_seq = 5, 9
+    case = AttnCase(H, KH, hd, bs, batch, blocks_per_seq, blocks_per_seq, num_layers=2)
+    case.kv_cache = normal_f32(case.kv_cache.size, 11, 1.0)
+    q = normal_f32(batch * H * hd, 12, 1.0)
+    pos = [int(p) for p in rng.integers(0, blocks_per_seq * bs, batch)]
+    pos[0], pos[1] = 0, blocks_per_seq * bs - 1
+    for window in (None, 3 * bs + 1):
+        st = case.starts(pos, window)
+        for layer in (0, 1):
+            close(gpu_run(ctx, case, q, case.tables, pos, st, layer), cpu_run(oracle, case, q, case.tables, pos, st, layer))
+
+
+def test_long_contexts_split_the_kv_axis(ctx, oracle):
+    """Contexts long enough that one (sequence, kv head) is spread over several CTAs."""
+    H, KH, hd, bs = 32, 4, 64, 16
+    batch, blocks = 3, 160
+    case = AttnCase(H, KH, hd, bs, batch, blocks, blocks)
+    case.kv_cache = normal_f32(case.kv_cache.size, 5, 1.0)
+    q = normal_f32(batch * H * hd, 6, 1.0)
+    pos = [2559, 1030, 300]
+    got = gpu_run(ctx, case, q, case.tables, pos, [0, 0, 0])
+    close(got, cpu_run(oracle, case, q, case.tables, pos, [0, 0, 0]))
+    got = gpu_run(ctx, case, q, case.tables, pos, [1500, 0, 299])
+    close(got, cpu_run(oracle, case, q, case.tables, pos, [1500, 0, 299]))
+
+
+def test_kv_pool_roundtrip_copy_block_and_token_io(ctx, oracle):
+    from paged_infer_b200 import api
+    for (nl, nb, bs, kh, hd) in [(3, 5, 16, 4, 64), (2, 4, 8, 2, 24), (1, 3, 1, 1, 1)]:
+        L = api.KvLayout(nl, nb, bs, kh, hd)
+        host = normal_f32(L.total_floats(), 1, 1.0)
+        kv = api.KvCache(ctx, L)
+        kv.upload(host)
+        assert np.array_equal(kv.download(), host)
+        # copy-on-write copy across all layers == the reference's copy_block (layout.rs:82-96)
+        want = host.copy()
+        oracle.kv_copy_block(oracle.kv_layout(nl, nb, bs, kh, hd), want, 1, nb - 1)
+        kv.copy_block(1, nb - 1)
+        assert np.array_equal(kv.download(), want)
+        with pytest.raises(api.PiError):
+            kv.copy_block(2, 2)
+        with pytest.raises(api.PiError):
+            kv.copy_block(0, nb)
+        k, v = normal_f32(kh * hd, 2), normal_f32(kh * hd, 3)
+        kv.write_token(nl - 1, 0, bs - 1, k, v)
+        rk, rv = kv.read_token(nl - 1, 0, bs - 1)
+        assert np.array_equal(rk, k) and np.array_equal(rv, v)
+        d = kv.download()
+        for h in range(kh):
+            i = L.index(nl - 1, 0, bs - 1, h, False)
+            assert np.array_equal(d[i:i + hd], k[h * hd:(h + 1) * hd])
+            j = L.index(nl - 1, 0, bs - 1, h, True)
+            assert np.array_equal(d[j:j + hd], v[h * hd:(h + 1) * hd])
+
+
+def test_bad_head_grouping_is_an_error(ctx):
+    from paged_infer_b200 import api
+    L = api.KvLayout(1, 4, 8, 3, 4)
+    kv = api.KvCache(ctx, L)
+    with pytest.raises(api.PiError):  # 8 heads over 3 kv heads (attention.rs:159-165)
+        api.PagedAttention(L, 8).run(np.zeros(8 * 4, np.float32), kv, [api.AttnEntry(api.BlockTable([0]), 3)])
+    with pytest.raises(api.PiError):  # physical block outside the pool
+        api.PagedAttention(L, 6).run(np.zeros(6 * 4, np.float32), kv, [api.AttnEntry(api.BlockTable([9]), 3)])
