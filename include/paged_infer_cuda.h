@@ -82,6 +82,15 @@ pi_status pi_ctx_synchronize(pi_ctx* ctx);
 /* Kernels launched by this context since creation (or since the last reset). */
 uint64_t pi_ctx_kernel_launches(const pi_ctx* ctx);
 void pi_ctx_reset_kernel_launches(pi_ctx* ctx);
+/* Per-kernel-class device timing.  Between begin and end every launch of the
+ * context is bracketed by CUDA events on its stream (which serialises
+ * launches that would otherwise overlap); end waits for the stream and returns,
+ * per class, the summed device time in milliseconds and the number of launches.
+ * Classes: */
+enum { PI_PROF_GEMV = 0, PI_PROF_GEMM_TC = 1, PI_PROF_ATTENTION = 2, PI_PROF_ROPE_KV = 3, PI_PROF_OTHER = 4,
+       PI_PROF_COLLECTIVE = 5, PI_PROF_CLASSES = 6 };
+pi_status pi_ctx_profile_begin(pi_ctx* ctx);
+pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out /*[PI_PROF_CLASSES]*/, uint64_t* launches_out /*[PI_PROF_CLASSES]*/);
 /* Tuning knobs (all default on): 0/1. */
 enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4 };
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value);
@@ -265,6 +274,23 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* model, pi_kv_pool* pool,
 pi_status pi_model_prefill(pi_ctx* ctx, pi_model* model, pi_kv_pool* pool, const uint32_t* tokens_host, int n,
                            int start_pos, const int32_t* block_table_host, int table_len, int chunk,
                            float* last_logits_host_or_null, uint32_t* argmax_host_or_null);
+
+/* n_steps greedy decode steps of the same B sequences without returning to the
+ * host in between: step s feeds the argmax of step s-1 at position
+ * positions[b] + s.  The block tables must already map every position that
+ * will be written (an unmapped position's K/V write is skipped, as always).
+ * out_tokens_host receives [n_steps][B] token ids.
+ * Replaces: n_steps iterations of Engine::step's decode phase for sequences
+ * sampled greedily (src/engine.rs:602-761 with temperature 0), minus the host
+ * bookkeeping between them. */
+pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* model, pi_kv_pool* pool,
+                                const uint32_t* tokens_host, const int32_t* positions_host,
+                                const int32_t* block_tables_host, int max_blocks, const int32_t* table_lens_host,
+                                int B, int n_steps, uint32_t* out_tokens_host);
+
+/* Fill the whole pool with N(0, std) values (synthetic KV for benchmarks).
+ * No counterpart in the reference. */
+pi_status pi_kv_fill_normal(pi_ctx* ctx, pi_kv_pool* pool, uint64_t seed, float std);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,7 @@ PI_ERR_UNSUPPORTED = -6
 
 PI_SPLIT_NONE, PI_SPLIT_COLUMN, PI_SPLIT_ROW = 0, 1, 2
 PI_F32, PI_INT8, PI_BF16 = 0, 1, 2
+PROF_CLASSES = ("gemv", "gemm_tc", "attention", "rope_kv", "other", "collective")
 PI_OPT_TENSOR_GEMM, PI_OPT_CUDA_GRAPH, PI_OPT_PDL, PI_OPT_GEMV_MAX_M = 1, 2, 3, 4
 
 
@@ -73,6 +74,8 @@ SIGNATURES = {
     "pi_ctx_kernel_launches": (C.c_uint64, [_P]),
     "pi_ctx_reset_kernel_launches": (None, [_P]),
     "pi_ctx_set_option": (_I, [_P, _I, _I]),
+    "pi_ctx_profile_begin": (_I, [_P]),
+    "pi_ctx_profile_end": (_I, [_P, _P, _P]),
     "pi_quantize_rows_i8": (_I, [_P, _P, _SZ, _SZ, _P, _P]),
     "pi_quantize_rows_i8_dev": (_I, [_P, _P, _SZ, _SZ, _P, _P]),
     "pi_linear_create_i8": (_I, [_P, _SZ, _SZ, _P, _P, _I, _PP]),
@@ -107,6 +110,8 @@ SIGNATURES = {
     "pi_model_weight_bytes": (_SZ, [_P]),
     "pi_model_decode_batch": (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "pi_model_prefill": (_I, [_P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _P]),
+    "pi_model_decode_multi": (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P]),
+    "pi_kv_fill_normal": (_I, [_P, _P, C.c_uint64, C.c_float]),
 }
 
 _lib = None

@@ -72,6 +72,18 @@ class Context:
     def reset_kernel_launches(self):
         _lib.lib().pi_ctx_reset_kernel_launches(self.handle)
 
+    def profile_begin(self):
+        """Start bracketing every launch with CUDA events (per kernel class)."""
+        check(_lib.lib().pi_ctx_profile_begin(self.handle), self.handle)
+
+    def profile_end(self) -> dict:
+        """{class: (device ms, launches)} since :meth:`profile_begin`."""
+        n = len(_lib.PROF_CLASSES)
+        ms = (C.c_double * n)()
+        cnt = (C.c_uint64 * n)()
+        check(_lib.lib().pi_ctx_profile_end(self.handle, ms, cnt), self.handle)
+        return {name: (float(ms[i]), int(cnt[i])) for i, name in enumerate(_lib.PROF_CLASSES)}
+
     def set_option(self, option: int, value: int):
         check(_lib.lib().pi_ctx_set_option(self.handle, option, value), self.handle)
 
@@ -340,6 +352,10 @@ class KvCache:
         check(_lib.lib().pi_kv_download(self.ctx.handle, self.handle, _ptr(out)), self.ctx.handle)
         return out
 
+    def fill_normal(self, seed: int, std: float = 1.0):
+        """Synthetic N(0, std) contents for benchmarks."""
+        check(_lib.lib().pi_kv_fill_normal(self.ctx.handle, self.handle, seed, std), self.ctx.handle)
+
     def write_token(self, layer: int, block: int, tok: int, k, v):
         k, v = _f32(k), _f32(v)
         check(_lib.lib().pi_kv_write_token(self.ctx.handle, self.handle, layer, block, tok, _ptr(k), _ptr(v)), self.ctx.handle)
@@ -499,6 +515,17 @@ class LlamaWeights:
         if want_logits and want_argmax:
             return logits, ids
         return logits if want_logits else ids
+
+    def decode_multi(self, tokens, positions, block_tables, kv_cache: KvCache, n_steps: int) -> np.ndarray:
+        """``n_steps`` greedy decode steps without host round trips; returns token ids [n_steps, B]."""
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        positions = _i32(positions)
+        B = tokens.size
+        mat, lens, mb = pack_block_tables(block_tables)
+        out = np.empty((n_steps, B), np.uint32)
+        check(_lib.lib().pi_model_decode_multi(self.ctx.handle, self.handle, kv_cache.handle, _ptr(tokens), _ptr(positions),
+                                               _ptr(mat), mb, _ptr(lens), B, n_steps, _ptr(out)), self.ctx.handle)
+        return out
 
     def forward(self, token_id: int, pos: int, block_table, kv_cache: KvCache) -> np.ndarray:
         """``LlamaWeights::forward`` (src/model.rs:630-652): one token, logits [vocab]."""

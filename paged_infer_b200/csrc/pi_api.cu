@@ -25,6 +25,22 @@ pi_status pi_fail(pi_ctx* ctx, pi_status code, const char* fmt, ...) {
   return code;
 }
 
+pi_prof_scope::pi_prof_scope(pi_ctx* c, int cls) : ctx(c), slot(-1) {
+  if (!c->prof_on || c->prof_used >= (1u << 16)) return;
+  if (c->prof_events.size() < 2 * (c->prof_used + 1)) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    c->prof_events.push_back(a);
+    c->prof_events.push_back(b);
+  }
+  slot = (long)c->prof_used++;
+  c->prof_class.push_back(cls);
+  cudaEventRecord(c->prof_events[2 * slot], c->stream);
+}
+pi_prof_scope::~pi_prof_scope() {
+  if (slot >= 0) cudaEventRecord(ctx->prof_events[2 * slot + 1], ctx->stream);
+}
+
 pi_status pi_reserve(pi_ctx* ctx, pi_buffer* buf, size_t bytes) {
   if (bytes <= buf->bytes) return PI_OK;
   // The old allocation may still be in use by queued kernels.
@@ -142,6 +158,7 @@ void pi_ctx_destroy(pi_ctx* ctx) {
                        &ctx->gemm_act, &ctx->gemm_partial})
     if (b->ptr) cudaFree(b->ptr);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
   if (ctx->dev_err) cudaFree(ctx->dev_err);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -156,6 +173,34 @@ pi_status pi_ctx_synchronize(pi_ctx* ctx) {
 uint64_t pi_ctx_kernel_launches(const pi_ctx* ctx) { return ctx ? ctx->launches : 0; }
 void pi_ctx_reset_kernel_launches(pi_ctx* ctx) {
   if (ctx) ctx->launches = 0;
+}
+
+pi_status pi_ctx_profile_begin(pi_ctx* ctx) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->prof_on = true;
+  ctx->prof_used = 0;
+  ctx->prof_class.clear();
+  return PI_OK;
+}
+
+pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out, uint64_t* launches_out) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, ms_out && launches_out, "null pointer");
+  ctx->prof_on = false;
+  PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int c = 0; c < PI_PROF_CLASSES; ++c) {
+    ms_out[c] = 0.0;
+    launches_out[c] = 0;
+  }
+  for (size_t i = 0; i < ctx->prof_used; ++i) {
+    float ms = 0.f;
+    PI_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]));
+    ms_out[ctx->prof_class[i]] += ms;
+    launches_out[ctx->prof_class[i]] += 1;
+  }
+  ctx->prof_used = 0;
+  return PI_OK;
 }
 
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
@@ -438,6 +483,14 @@ pi_status pi_kv_copy_block(pi_ctx* ctx, pi_kv_pool* pool, int32_t src, int32_t d
   PI_REQUIRE(ctx, src >= 0 && src < pool->L.num_blocks && dst >= 0 && dst < pool->L.num_blocks,
              "block %d -> %d outside the pool's %d blocks", src, dst, pool->L.num_blocks);
   return pi_launch_copy_block(ctx, pool, src, dst);
+}
+
+pi_status pi_kv_fill_normal(pi_ctx* ctx, pi_kv_pool* pool, uint64_t seed, float std) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, pool, "null pool");
+  PI_TRY(pi_launch_fill_normal(ctx, pool->data, pool->floats, seed, 0xCAC4Eull, 0, std));
+  PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return PI_OK;
 }
 
 pi_status pi_kv_upload(pi_ctx* ctx, pi_kv_pool* pool, const float* cache_host) {

@@ -347,6 +347,7 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   p.part_ml = nullptr;
   p.part_acc = nullptr;
 
+  pi_prof_scope prof(ctx, PI_PROF_ATTENTION);
   const bool fast = (HD == 64 || HD == 128) && (group == 1 || group == 2 || group == 4 || group == 8) &&
                     ((uintptr_t)q % 16 == 0) && (q_stride % 4 == 0);
   cudaError_t e;

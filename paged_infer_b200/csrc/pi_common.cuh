@@ -73,6 +73,12 @@ struct pi_ctx {
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
 
+  // per-kernel-class timing with CUDA events on this stream (off by default)
+  bool prof_on = false;
+  std::vector<cudaEvent_t> prof_events;  // 2 per recorded launch
+  std::vector<int> prof_class;
+  size_t prof_used = 0;
+
   // scratch
   pi_buffer staging_in, staging_out;   // device copies of host arguments / results
   pi_buffer attn_tables, attn_meta;    // block tables + per-entry (len, pos, start)
@@ -81,6 +87,14 @@ struct pi_ctx {
   pi_buffer gemm_partial;              // split-K partial sums
   void* pinned = nullptr;              // pinned host staging
   size_t pinned_bytes = 0;
+};
+
+// Brackets one launch (or one short launch sequence) with events while profiling is on.
+struct pi_prof_scope {
+  pi_ctx* ctx;
+  long slot;
+  pi_prof_scope(pi_ctx* c, int cls);
+  ~pi_prof_scope();
 };
 
 pi_status pi_reserve(pi_ctx* ctx, pi_buffer* buf, size_t bytes);

@@ -361,9 +361,9 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
   for (int c = threadIdx.x; c < (int)q_ld; c += blockDim.x) {
     int8_t code = 0;
     if (c < cols) {
-      float v = roundf(__fdiv_rn(src[c], scale));  // half away from zero, true division
-      v = fminf(fmaxf(v, -127.0f), 127.0f);        // NaN survives to the cast below, as in Rust's clamp
-      code = (v != v) ? (int8_t)0 : (int8_t)(int)v;
+      const float v = roundf(__fdiv_rn(src[c], scale));  // half away from zero, true division
+      // Rust's clamp keeps NaN and `as i8` maps it to 0; fminf/fmaxf would drop the NaN instead.
+      code = (v != v) ? (int8_t)0 : (int8_t)(int)fminf(fmaxf(v, -127.0f), 127.0f);
     }
     dst[c] = code;  // padding columns are zero
   }
@@ -412,6 +412,7 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
   p.use_tma = ((lin->cols * sizeof(float)) % 16 == 0) && ((uintptr_t)a.x % 16 == 0) &&
               ((a.x_stride * sizeof(float)) % 16 == 0) && ((size_t)mb * lin->cols * sizeof(float) < (1u << 20));
   const bool norm = a.norm_weight != nullptr;
+  pi_prof_scope prof(ctx, PI_PROF_GEMV);
   cudaError_t e;
   if (lin->kind == PI_INT8)
     e = launch_gemv_w<int8_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);

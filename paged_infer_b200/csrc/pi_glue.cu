@@ -282,6 +282,7 @@ void pi_host_rope_table(int pos, int head_dim, float theta, float* cos_out, floa
 
 pi_status pi_launch_embed(pi_ctx* ctx, const uint16_t* table_bf16, int vocab, int hidden, const uint32_t* tokens_dev,
                           int B, float* x) {
+  pi_prof_scope prof(ctx, PI_PROF_OTHER);
   PI_LAUNCHED(ctx, launch_pdl(ctx, embed_kernel, dim3(B), dim3(256), table_bf16, vocab, hidden, tokens_dev, x));
   return PI_OK;
 }
@@ -296,6 +297,7 @@ pi_status pi_launch_rope_kv_write(pi_ctx* ctx, float* qkv, size_t qkv_stride, in
                                   int head_dim, const float* rope_cos, const float* rope_sin, int style,
                                   pi_kv_pool* pool, int layer, const pi_attn_batch& batch) {
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
+  pi_prof_scope prof(ctx, PI_PROF_ROPE_KV);
   PI_LAUNCHED(ctx, launch_pdl(ctx, rope_kv_write_kernel, dim3(num_heads + num_kv_heads, batch.B), dim3(threads), qkv,
                               qkv_stride, num_heads, num_kv_heads, head_dim, rope_cos, rope_sin, style, pool->data,
                               pool->L, layer, batch.tables, batch.max_blocks, batch.lens, batch.pos));
@@ -317,12 +319,14 @@ pi_status pi_launch_swiglu(pi_ctx* ctx, float* gate, const float* up, size_t n) 
 }
 
 pi_status pi_launch_add(pi_ctx* ctx, float* x, const float* y, size_t n) {
+  pi_prof_scope prof(ctx, PI_PROF_OTHER);
   if (n == 0) return PI_OK;
   PI_LAUNCHED(ctx, launch_pdl(ctx, add_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), x, y, n));
   return PI_OK;
 }
 
 pi_status pi_launch_argmax(pi_ctx* ctx, const float* logits, size_t stride, int rows, int n, uint32_t* out) {
+  pi_prof_scope prof(ctx, PI_PROF_OTHER);
   PI_LAUNCHED(ctx, launch_pdl(ctx, argmax_kernel, dim3(rows), dim3(1024), logits, stride, n, out));
   return PI_OK;
 }

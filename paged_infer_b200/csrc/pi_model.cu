@@ -550,6 +550,55 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
   return PI_OK;
 }
 
+// After a greedy step: the chosen ids become the next inputs, every sequence moves on one position.
+static __global__ void advance_kernel(uint32_t* tokens, const uint32_t* chosen, uint32_t* history, int32_t* pos,
+                                      int32_t* start, int window, int B) {
+  pi_grid_dependency_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint32_t t = chosen[b];
+  tokens[b] = t;
+  history[b] = t;
+  const int p = pos[b] + 1;
+  pos[b] = p;
+  start[b] = window < 0 ? 0 : max(0, p + 1 - window);
+}
+
+pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host,
+                                const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,
+                                const int32_t* table_lens_host, int B, int n_steps, uint32_t* out_tokens_host) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, m && tokens_host && positions_host && table_lens_host && out_tokens_host, "null pointer");
+  PI_REQUIRE(ctx, block_tables_host || max_blocks == 0, "null block tables");
+  PI_REQUIRE(ctx, B > 0, "decode needs at least one sequence");
+  PI_REQUIRE(ctx, B <= m->capacity, "batch %d exceeds scratch capacity %d", B, m->capacity);
+  PI_REQUIRE(ctx, n_steps > 0, "n_steps must be positive");
+  PI_TRY(check_pool(ctx, m, pool));
+  int max_pos = 0;
+  for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, positions_host[b]);
+  PI_TRY(ensure_rope(ctx, m, max_pos + n_steps));
+  PI_TRY(pi_reserve(ctx, &ctx->staging_out, (size_t)n_steps * B * sizeof(uint32_t)));
+  uint32_t* history = static_cast<uint32_t*>(ctx->staging_out.ptr);
+  pi_attn_batch batch;
+  PI_TRY(stage_batch(ctx, m, pool, tokens_host, positions_host, block_tables_host, max_blocks, table_lens_host, B, &batch));
+  // The KV split is planned on the host from the final positions, so that every step fits it.
+  const int bs = pool->L.block_size;
+  batch.total_window_blocks += (long)B * ((n_steps + bs - 1) / bs);
+  batch.max_window_blocks += (n_steps + bs - 1) / bs;
+  for (int s = 0; s < n_steps; ++s) {
+    PI_TRY(run_layers(ctx, m, pool, batch, B));
+    PI_TRY(project_logits(ctx, m, 0, B));
+    PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
+    pi_prof_scope prof(ctx, PI_PROF_OTHER);
+    advance_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(m->tokens_dev, m->argmax_dev, history + (size_t)s * B,
+                                                             const_cast<int32_t*>(batch.pos),
+                                                             const_cast<int32_t*>(batch.start), m->cfg.attention_window, B);
+    PI_CHECK_LAUNCH(ctx);
+  }
+  PI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, history, (size_t)n_steps * B * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  return pi_ctx_synchronize(ctx);
+}
+
 pi_status pi_model_prefill(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host, int n, int start_pos,
                            const int32_t* block_table_host, int table_len, int chunk, float* last_logits_host_or_null,
                            uint32_t* argmax_host_or_null) {

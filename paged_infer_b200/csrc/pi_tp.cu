@@ -84,6 +84,7 @@ void pi_tp_destroy(pi_ctx* ctx) {
 
 pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n) {
   if (ctx->tp == 1 || n == 0) return PI_OK;
+  pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
   PI_NCCL(ctx, nccl()->AllReduce(buf, buf, n, ncclFloat32, ncclSum, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->stream));
   return PI_OK;
 }

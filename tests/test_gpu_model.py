@@ -116,6 +116,7 @@ def test_batched_decode_equals_single_sequence(ctx, oracle):  # batched_decode_t
         okv = np.zeros(kv_floats(cfg, 3 * len(lens)), np.float32)
         gkv_b = api.KvCache(ctx, gm.kv_layout(3 * len(lens), BLOCK))
         gkv_s = api.KvCache(ctx, gm.kv_layout(3 * len(lens), BLOCK))
+        gkv_b.upload(okv)  # the pool starts undefined; the oracle's cache starts at zero
         for b, n in enumerate(lens):
             om.prefill(tokens[:n], 0, tables[b], okv, BLOCK)
             gm.prefill_batched(tokens[:n], 0, tables[b], gkv_b, 8)
