@@ -1,7 +1,575 @@
-// Tensor-core (tcgen05 / TMEM) dequant GEMM for batched decode and prefill.
+// Tensor-core dequant GEMM for batched decode and prefill: tcgen05.mma with the
+// accumulator in tensor memory (TMEM), for int8 weights and f32 activations.
+//
+//   out[m][r] = scale[r] * sum_k W[r][k] * x[m][k]
+//
+// Swap-AB: the 128 weight rows of a CTA sit on the MMA's M axis, the batch on
+// its N axis (16..128 per CTA).  The int8 weight tile is widened to fp16 (exact)
+// in registers and written to shared memory in the 128-byte-swizzled K-major
+// layout the MMA reads.  Each f32 activation is split into fp16 hi + fp16 lo
+// after a power-of-two row scaling (x*s = hi + lo up to 2^-25 of the row's
+// largest element); both planes are fetched by TMA (cp.async.bulk.tensor, no
+// multicast) and the tile gets two MMAs per K step, which keeps the result
+// f32-equivalent: every product is exact and accumulation is in f32.
+//
+// Warp roles (10 warps): 0-7 stream + widen the weights and later run the
+// epilogue out of TMEM; warp 8 issues the TMA loads of the activations; warp 9
+// allocates TMEM and issues the MMAs.  Stages are handed over with mbarriers;
+// every wait is bounded and a wait that runs out raises the context's error
+// word instead of hanging.
+//
+// K is split across CTAs when there are too few row tiles to fill the SMs; the
+// last CTA to finish a tile adds the partial sums in a fixed order, so results
+// do not depend on timing.
+//
+// Replaces math::matmat_i8_weight_parallel + transpose_rb_to_br for batches
+// beyond a few rows (reference src/math.rs:223-290).
+#include <cuda.h>
+
+#include <algorithm>
+
 #include "pi_common.cuh"
 
-bool pi_gemm_tc_supported(const pi_ctx*, const pi_linear*, const pi_linear_args&) { return false; }
-pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear*, const pi_linear_args&) {
-  return pi_fail(ctx, PI_ERR_UNSUPPORTED, "tensor-core GEMM is not available for this shape");
+namespace {
+
+constexpr int kBM = 128;            // weight rows per CTA (MMA M)
+constexpr int kBK = 128;            // K elements per pipeline stage (two 128-byte swizzle atoms of fp16)
+constexpr int kProducerWarps = 8;
+constexpr int kThreads = (kProducerWarps + 2) * 32;
+constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr int kATileBytes = kBM * kBK * 2;  // 32 KiB of fp16 per stage
+
+struct GemmParams {
+  const int8_t* W;
+  const float* scales;      // [N]
+  const float* act_scale;   // [M] power-of-two factors to multiply back
+  float* out;
+  size_t ld, out_stride;
+  int N, K, M;
+  int ksplit, nkb;          // K splits, total K blocks
+  int epi;
+  float* partial;           // [ksplit][M_pad][N_pad] when ksplit > 1
+  int* counters;            // one per (row tile, batch tile)
+  size_t part_row_stride;   // N_pad
+  size_t part_split_stride; // M_pad * N_pad
+  int* err_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ int4 ld_stream_16(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// 4 int8 -> 4 fp16 (exact): byte b^0x80 into the mantissa of 1024.0, minus 1152.
+__device__ __forceinline__ void widen4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t x = w ^ 0x80808080u;
+  const uint32_t a = __byte_perm(x, 0x64646464u, 0x4140);
+  const uint32_t b = __byte_perm(x, 0x64646464u, 0x4342);
+  const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));  // 1152.0
+  __half2 ha = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
+  __half2 hb = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
+  lo = *reinterpret_cast<uint32_t*>(&ha);
+  hi = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);       // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// One output value through the epilogue.  SwiGLU pairs (gate, up) sit in adjacent rows = adjacent lanes.
+__device__ __forceinline__ void emit(const GemmParams& p, int m, int row, float v, int lane) {
+  if (p.epi == PI_EPI_SWIGLU) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+    if (!(lane & 1) && m < p.M && row + 1 < p.N) p.out[(size_t)m * p.out_stride + (row >> 1)] = silu_mul(v, other);
+  } else if (m < p.M && row < p.N) {
+    float* o = p.out + (size_t)m * p.out_stride + row;
+    *o = (p.epi == PI_EPI_ADD) ? (*o + v) : v;
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo) {
+  constexpr int kBTileBytes = 2 * BN * 128;                 // one plane, two swizzle atoms
+  constexpr int kStageBytes = kATileBytes + 2 * kBTileBytes;
+  constexpr int kTmemCols = BN < 32 ? 32 : BN;              // power of two >= 32
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ uint32_t s_tmem;
+  __shared__ volatile int s_abort;
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
+  const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, kProducerWarps * 32 + 1);  // every producer thread + the TMA thread's expect_tx
+      mbar_init(empty0 + 8 * s, 1);                        // one tcgen05.commit
+    }
+    mbar_init(accum_bar, 1);
+    s_abort = 0;
+    s_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == kProducerWarps + 1) {  // TMEM allocation is warp-wide
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  const uint32_t smem_base = smem_u32(smem);
+
+  pi_grid_dependency_wait();
+
+  if (warp < kProducerWarps) {
+    // ---- weight producers: 16 KiB of int8 per stage, 4 x 16 bytes per thread ----------------------
+    // chunk c = i*256 + tid covers row c/8, bytes (c%8)*16..+16 of the stage's 128 K elements.
+    const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.W);
+    const unsigned char* src[4];
+    uint32_t dst[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = i * 256 + tid, r = c >> 3, kc = c & 7;
+      const int row = min(row0 + r, p.N - 1);
+      src[i] = wbase + (size_t)row * p.ld + kc * 16;
+      // 16 int8 -> 32 bytes of fp16 = chunks 2*(kc&3), 2*(kc&3)+1 of atom kc>>2, XOR-swizzled by the row
+      dst[i] = (uint32_t)((kc >> 2) * (kBM * 128) + r * 128) | ((uint32_t)(r & 7) << 16) | ((uint32_t)(kc & 3) << 24);
+    }
+    int4 cur[4], nxt[4];
+    if (kb_begin < kb_end) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cur[i] = ld_stream_16(src[i] + (size_t)kb_begin * kBK);
+    }
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+      const int it = kb - kb_begin, s = it % STAGES;
+      if (kb + 1 < kb_end) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) nxt[i] = ld_stream_16(src[i] + (size_t)(kb + 1) * kBK);
+      }
+      if (s_abort) break;
+      if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+        s_abort = 1;
+        if (p.err_flag) atomicExch(p.err_flag, 2);
+        break;
+      }
+      const uint32_t a_stage = smem_base + s * kStageBytes;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t h[8];
+        widen4((uint32_t)cur[i].x, h[0], h[1]);
+        widen4((uint32_t)cur[i].y, h[2], h[3]);
+        widen4((uint32_t)cur[i].z, h[4], h[5]);
+        widen4((uint32_t)cur[i].w, h[6], h[7]);
+        const uint32_t rowbase = a_stage + (dst[i] & 0xFFFF), sw = (dst[i] >> 16) & 7, c0 = ((dst[i] >> 24) & 3) * 2;
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + ((c0 ^ sw) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + (((c0 + 1) ^ sw) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+      mbar_arrive(full0 + 8 * s);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+    }
+  } else if (warp == kProducerWarps) {
+    // ---- activation loader: TMA, hi and lo planes, two 64-column boxes each ---------------------------
+    if (lane == 0) {
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin, s = it % STAGES;
+        if (s_abort) break;
+        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+          s_abort = 1;
+          if (p.err_flag) atomicExch(p.err_flag, 3);
+          break;
+        }
+        const uint32_t bar = full0 + 8 * s;
+        const uint32_t b_stage = smem_base + s * kStageBytes + kATileBytes;
+        mbar_arrive_expect_tx(bar, 2 * kBTileBytes);
+#pragma unroll
+        for (int plane = 0; plane < 2; ++plane) {
+          const CUtensorMap* map = plane == 0 ? &map_hi : &map_lo;
+#pragma unroll
+          for (int atom = 0; atom < 2; ++atom) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                    b_stage + plane * kBTileBytes + atom * (BN * 128)),
+                "l"(map), "r"(bar), "r"(kb * kBK + atom * 64), "r"(m0)
+                : "memory");
+          }
+        }
+      }
+    }
+  } else {
+    // ---- MMA issuer ------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      // kind::f16, D = f32, A and B = f16, both K-major, N = BN, M = 128
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin, s = it % STAGES;
+        if (s_abort || !mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) {
+          if (!s_abort && p.err_flag) atomicExch(p.err_flag, 4);
+          s_abort = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_stage = smem_base + s * kStageBytes, b_hi = a_stage + kATileBytes, b_lo = b_hi + kBTileBytes;
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {  // 16 K elements = 32 bytes per MMA
+            const uint64_t da = smem_desc(a_stage + atom * (kBM * 128) + ks * 32);
+            const uint64_t dh = smem_desc(b_hi + atom * (BN * 128) + ks * 32);
+            const uint64_t dl = smem_desc(b_lo + atom * (BN * 128) + ks * 32);
+            umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
+            umma_f16(tmem, da, dl, idesc, 1u);
+          }
+        }
+        umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  }
+
+  // ---- epilogue: warps 0-7 read the accumulator (warp w owns TMEM lanes 32*(w%4).., columns split in halves) ----
+  bool have_acc = false;
+  if (warp < kProducerWarps) {
+    have_acc = (kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0);
+    if (kb_begin < kb_end && !have_acc && !s_abort) {
+      s_abort = 1;
+      if (lane == 0 && p.err_flag) atomicExch(p.err_flag, 5);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  const int quad = warp & 3, half = warp >> 2;
+  const int row = row0 + quad * 32 + lane;
+  constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
+  const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
+
+  if (p.ksplit == 1) {
+    if (epi_warp && have_acc) {
+      const float ws = row < p.N ? p.scales[row] : 0.f;
+#pragma unroll 1
+      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c0 + j;
+          const float as = m < p.M ? p.act_scale[m] : 0.f;
+          emit(p, m, row, v[j] * ws * as, lane);
+        }
+      }
+    }
+  } else {
+    // write this split's raw partial sums, then let the last CTA of the tile add them in order
+    if (epi_warp) {
+      float* part = p.partial + (size_t)blockIdx.y * p.part_split_stride;
+#pragma unroll 1
+      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+        float v[16];
+        if (have_acc) {
+          tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(size_t)(m0 + c0 + j) * p.part_row_stride + row0 + quad * 32 + lane] = v[j];
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int idx = blockIdx.z * gridDim.x + blockIdx.x;
+      const int prev = atomicAdd(&p.counters[idx], 1);
+      s_last = (prev == p.ksplit - 1);
+      if (s_last) p.counters[idx] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (s_last && epi_warp) {
+      __threadfence();
+      const float ws = row < p.N ? p.scales[row] : 0.f;
+#pragma unroll 1
+      for (int c = half * kColsPerHalf; c < (half + 1) * kColsPerHalf && c < BN; ++c) {
+        const int m = m0 + c;
+        float acc = 0.f;
+        for (int ks = 0; ks < p.ksplit; ++ks)
+          acc += __ldcg(p.partial + (size_t)ks * p.part_split_stride + (size_t)m * p.part_row_stride + row0 + quad * 32 + lane);
+        const float as = m < p.M ? p.act_scale[m] : 0.f;
+        emit(p, m, row, acc * ws * as, lane);
+      }
+    }
+  }
+  pi_grid_launch_dependents();
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kProducerWarps + 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
+// ---- activation preparation: optional RMSNorm, power-of-two row scaling, fp16 hi/lo split ---------------------
+__global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict__ x, size_t x_stride,
+                                                        const float* __restrict__ norm_weight, float eps, int K,
+                                                        __half* __restrict__ hi, __half* __restrict__ lo,
+                                                        float* __restrict__ act_scale) {
+  extern __shared__ float ys[];
+  __shared__ float red[8];
+  __shared__ float s_val;
+  pi_grid_dependency_wait();
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const float* row = x + (size_t)m * x_stride;
+  float inv = 1.0f;
+  if (norm_weight) {
+    float ss = 0.f;
+    for (int k = tid; k < K; k += blockDim.x) ss = fmaf(row[k], row[k], ss);
+    ss = pi_warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+      s_val = 1.0f / sqrtf(t / (float)K + eps);
+    }
+    __syncthreads();
+    inv = s_val;
+    __syncthreads();
+  }
+  float mx = 0.f;
+  for (int k = tid; k < K; k += blockDim.x) {
+    const float y = norm_weight ? row[k] * inv * norm_weight[k] : row[k];
+    ys[k] = y;
+    mx = fmaxf(mx, fabsf(y));
+  }
+  mx = pi_warp_max(mx);
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t = fmaxf(t, red[i]);
+    int e = 0;
+    if (t > 0.f && t < INFINITY) frexpf(t, &e);   // t = f * 2^e, f in [0.5, 1)
+    s_val = ldexpf(1.0f, -e);                     // scaled row max lands in [0.5, 1)
+    act_scale[m] = ldexpf(1.0f, e);
+  }
+  __syncthreads();
+  const float s = s_val;
+  for (int k = tid; k < K; k += blockDim.x) {
+    const float y = ys[k] * s;                    // exact: power-of-two scaling
+    const __half h = __float2half_rn(y);
+    hi[(size_t)m * K + k] = h;
+    lo[(size_t)m * K + k] = __float2half_rn(y - __half2float(h));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+int pick_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+template <int BN, int STAGES>
+cudaError_t launch_tc(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& hi, const CUtensorMap& lo, dim3 grid) {
+  constexpr size_t smem = (size_t)STAGES * (kATileBytes + 4 * BN * 128) + 1024;
+  auto k = gemm_tc_kernel<BN, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, k, p, hi, lo);
+}
+
+}  // namespace
+
+bool pi_gemm_tc_supported(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
+  (void)ctx;
+  if (lin->kind != PI_INT8) return false;
+  if (lin->cols % kBK != 0 || lin->ld != lin->cols) return false;   // whole K blocks, 16-byte aligned rows
+  if (lin->rows < 32) return false;
+  if (a.epi == PI_EPI_SWIGLU && (lin->rows % 2) != 0) return false;
+  if (lin->cols > 65536 * 2) return false;
+  return encode_tiled() != nullptr;
+}
+
+pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
+  PI_REQUIRE(ctx, pi_gemm_tc_supported(ctx, lin, a), "tensor-core GEMM does not support this projection");
+  const int M = a.M, K = (int)lin->cols, N = (int)lin->rows;
+  const int BN = pick_bn(M);
+  const int mtiles = (M + BN - 1) / BN, M_pad = mtiles * BN;
+  const int rtiles = (N + kBM - 1) / kBM, N_pad = rtiles * kBM;
+  const int nkb = K / kBK;
+
+  // K splits: aim at ~1.5 CTAs per SM, at least two K blocks each.
+  int ksplit = 1;
+  const int tiles = rtiles * mtiles;
+  if (tiles < ctx->sm_count) {
+    ksplit = std::min(std::max(1, (ctx->sm_count * 3 / 2) / tiles), std::max(1, nkb / 2));
+    ksplit = std::min(ksplit, 32);
+  }
+
+  // workspace: [act hi | act lo | act_scale] and [counters | partials]
+  const size_t plane = (size_t)M_pad * K * sizeof(__half);
+  PI_TRY(pi_reserve(ctx, &ctx->gemm_act, 2 * plane + (size_t)M_pad * sizeof(float) + 256));
+  __half* hi = static_cast<__half*>(ctx->gemm_act.ptr);
+  __half* lo = hi + (size_t)M_pad * K;
+  float* act_scale = reinterpret_cast<float*>(lo + (size_t)M_pad * K);
+  const size_t counters_bytes = 4096 * sizeof(int);
+  PI_REQUIRE(ctx, tiles <= 4096, "too many output tiles for the split-K counters");
+  const size_t part_bytes = ksplit > 1 ? (size_t)ksplit * M_pad * N_pad * sizeof(float) : 0;
+  if (ctx->gemm_partial.bytes < counters_bytes + part_bytes) {
+    PI_TRY(pi_reserve(ctx, &ctx->gemm_partial, counters_bytes + part_bytes));
+    PI_CUDA(ctx, cudaMemsetAsync(ctx->gemm_partial.ptr, 0, counters_bytes, ctx->stream));
+  }
+
+  pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (size_t)K * sizeof(float);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+    if (cfg.dynamicSmemBytes > 48 * 1024)
+      PI_CUDA(ctx, cudaFuncSetAttribute(act_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, act_split_kernel, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+    if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
+    ctx->launches++;
+  }
+
+  CUtensorMap maps[2];
+  for (int i = 0; i < 2; ++i) {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};          // innermost first; rows past M read as zero
+    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+    const cuuint32_t box[2] = {64, (cuuint32_t)BN};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled()(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, i == 0 ? (void*)hi : (void*)lo, dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return pi_fail(ctx, PI_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  }
+
+  GemmParams p;
+  p.W = static_cast<const int8_t*>(lin->w);
+  p.scales = lin->scales;
+  p.act_scale = act_scale;
+  p.out = a.out;
+  p.ld = lin->ld;
+  p.out_stride = a.out_stride;
+  p.N = N;
+  p.K = K;
+  p.M = M;
+  p.ksplit = ksplit;
+  p.nkb = nkb;
+  p.epi = a.epi;
+  p.counters = static_cast<int*>(ctx->gemm_partial.ptr);
+  p.partial = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_partial.ptr) + counters_bytes);
+  p.part_row_stride = N_pad;
+  p.part_split_stride = (size_t)M_pad * N_pad;
+  p.err_flag = ctx->dev_err;
+  const dim3 grid(rtiles, ksplit, mtiles);
+  cudaError_t e;
+  switch (BN) {
+    case 16: e = launch_tc<16, 4>(ctx, p, maps[0], maps[1], grid); break;
+    case 32: e = launch_tc<32, 4>(ctx, p, maps[0], maps[1], grid); break;
+    case 64: e = launch_tc<64, 3>(ctx, p, maps[0], maps[1], grid); break;
+    default: e = launch_tc<128, 2>(ctx, p, maps[0], maps[1], grid); break;
+  }
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
+  return PI_OK;
 }
