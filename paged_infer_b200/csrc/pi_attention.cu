@@ -46,6 +46,7 @@ struct AttnParams {
   float* part_ml;   // [B][H][nsplit][2]
   float* part_acc;  // [B][H][nsplit][HD]
   float scale;
+  int* err_flag;
 };
 
 __device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
@@ -188,6 +189,198 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const Attn
   }
 }
 
+// Same work split as attn_decode_kernel, but every (block, kv head) K|V tile - one contiguous
+// 2*block_size*HD*4-byte span of the pool - is brought into shared memory by a bulk async copy
+// (TMA, cp.async.bulk) through a per-warp ring of STAGES slots, so several tiles per warp are in
+// flight while one is being consumed.  A lane reads 16-byte chunks `li` and `li + LPT` of a token
+// row, which keeps the 128-bit shared loads free of bank conflicts.
+constexpr uint32_t kAttnSpinLimit = 1u << 21;
+
+__device__ __forceinline__ uint32_t attn_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int HD, int G, int STAGES>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_tma_kernel(const AttnParams p) {
+  constexpr int LPT = HD / 8;    // lanes per token
+  constexpr int TPW = 32 / LPT;  // tokens per warp step
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  __shared__ __align__(8) unsigned long long bars[kAttnWarps][STAGES];
+  __shared__ float s_m[kAttnWarps][G], s_l[kAttnWarps][G];
+
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tg = lane / LPT, li = lane % LPT;
+  const int BS = p.L.block_size;
+  const uint32_t tile_bytes = 2u * BS * HD * sizeof(float);
+  float* ring = reinterpret_cast<float*>(attn_smem) + (size_t)warp * STAGES * (tile_bytes / 4);
+
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(attn_smem_u32(&bars[warp][s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+  pi_grid_dependency_wait();
+
+  const int pos = p.pos[b], st = p.start[b], len = p.lens[b];
+  const int lb_first = st / BS, lb_last = pos / BS;
+  const int lb_begin = lb_first + split * p.blocks_per_cta;
+  const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);
+  const int nblk = (st <= pos && lb_begin + warp < lb_end) ? (lb_end - lb_begin - warp + kAttnWarps - 1) / kAttnWarps : 0;
+
+  auto issue = [&](int j) {  // lane 0 only: tile j of this warp -> slot j % STAGES
+    const int lb = lb_begin + warp + j * kAttnWarps;
+    const int pb = p.tables[(size_t)b * p.max_blocks + lb];
+    const float* src = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kvh, 0);
+    const uint32_t bar = attn_smem_u32(&bars[warp][j % STAGES]);
+    const uint32_t dst = attn_smem_u32(ring + (size_t)(j % STAGES) * (tile_bytes / 4));
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tile_bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(tile_bytes), "r"(bar)
+                 : "memory");
+  };
+  if (lane == 0)
+    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j);
+
+  float qv[G][8];
+  const float* qb = p.q + (size_t)b * p.q_stride + (size_t)kvh * G * HD;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float4 a = ldg_f4(qb + g * HD + li * 4), c = ldg_f4(qb + g * HD + (li + LPT) * 4);
+    qv[g][0] = a.x; qv[g][1] = a.y; qv[g][2] = a.z; qv[g][3] = a.w;
+    qv[g][4] = c.x; qv[g][5] = c.y; qv[g][6] = c.z; qv[g][7] = c.w;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+  }
+
+  bool failed = false;
+  for (int j = 0; j < nblk && !failed; ++j) {
+    const int slot = j % STAGES;
+    const uint32_t bar = attn_smem_u32(&bars[warp][slot]);
+    const uint32_t parity = (j / STAGES) & 1;
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < kAttnSpinLimit && !done; ++spin)
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (!__all_sync(0xffffffffu, done != 0)) {  // the copy never landed: report and stop (the result is not trusted)
+      if (lane == 0 && p.err_flag) atomicExch(p.err_flag, 6);
+      failed = true;
+      // give the copies still in flight one more bounded chance to land before the CTA's memory is released
+      for (int jj = j + 1; jj < nblk && jj < j + STAGES; ++jj) {
+        const uint32_t b2 = attn_smem_u32(&bars[warp][jj % STAGES]), par2 = (jj / STAGES) & 1;
+        uint32_t d2 = 0;
+        for (uint32_t spin = 0; spin < kAttnSpinLimit && !d2; ++spin)
+          asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                       : "=r"(d2) : "r"(b2), "r"(par2) : "memory");
+      }
+      break;
+    }
+    const int lb = lb_begin + warp + j * kAttnWarps;
+    const int t_lo = max(st - lb * BS, 0), t_hi = min(pos - lb * BS, BS - 1);
+    const float* Kt = ring + (size_t)slot * (tile_bytes / 4);
+    const float* Vt = Kt + (size_t)BS * HD;
+    for (int t0 = t_lo; t0 <= t_hi; t0 += TPW) {
+      const int t = t0 + tg;
+      const bool valid = t <= t_hi;
+      const int tc = valid ? t : t_hi;  // clamp: the row is in shared memory either way
+      const float4 k0 = *reinterpret_cast<const float4*>(Kt + (size_t)tc * HD + li * 4);
+      const float4 k1 = *reinterpret_cast<const float4*>(Kt + (size_t)tc * HD + (li + LPT) * 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(Vt + (size_t)tc * HD + li * 4);
+      const float4 v1 = *reinterpret_cast<const float4*>(Vt + (size_t)tc * HD + (li + LPT) * 4);
+      const float kx[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const float vx[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kx[i], d);
+#pragma unroll
+        for (int o = 1; o < LPT; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const float s = valid ? d * p.scale : -INFINITY;
+        if (s > m[g]) {
+          const float corr = lse_factor(m[g], s);
+          l[g] *= corr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] *= corr;
+          m[g] = s;
+        }
+        const float w = valid ? __expf(s - m[g]) : 0.f;
+        l[g] += w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(w, vx[i], acc[g][i]);
+      }
+    }
+    __syncwarp();  // every lane is done with the slot before it is refilled
+    if (lane == 0 && j + STAGES < nblk) issue(j + STAGES);
+  }
+
+  // merge the token groups of the warp
+#pragma unroll
+  for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o), lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float M = fmaxf(m[g], mo);
+      const float fs = lse_factor(m[g], M), fo = lse_factor(mo, M);
+      l[g] = l[g] * fs + lo * fo;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+        acc[g][i] = acc[g][i] * fs + ao * fo;
+      }
+      m[g] = M;
+    }
+  }
+  // The ring is free now (all copies were waited for): reuse its head as the cross-warp exchange buffer.
+  __syncthreads();
+  float* s_acc = reinterpret_cast<float*>(attn_smem);  // [warps][G][HD]
+  if (tg == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s_acc[((size_t)warp * G + g) * HD + li * 4 + i] = acc[g][i];
+        s_acc[((size_t)warp * G + g) * HD + (li + LPT) * 4 + i] = acc[g][4 + i];
+      }
+      if (li == 0) {
+        s_m[warp][g] = m[g];
+        s_l[warp][g] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  pi_grid_launch_dependents();
+  for (int idx = tid; idx < G * HD; idx += kAttnWarps * 32) {
+    const int g = idx / HD, d = idx - g * HD;
+    float M = s_m[0][g];
+#pragma unroll
+    for (int w = 1; w < kAttnWarps; ++w) M = fmaxf(M, s_m[w][g]);
+    float ls = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = lse_factor(s_m[w][g], M);
+      ls += s_l[w][g] * f;
+      a += s_acc[((size_t)w * G + g) * HD + d] * f;
+    }
+    const int h = kvh * G + g;
+    if (p.nsplit == 1) {
+      p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = a * (1.0f / fmaxf(ls, 1e-12f));
+    } else {
+      const size_t slot = ((size_t)b * p.H + h) * p.nsplit + split;
+      p.part_acc[slot * HD + d] = a;
+      if (d == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = ls;
+      }
+    }
+  }
+}
+
 // grid (H, B), HD threads (rounded up to a warp): merge the KV splits.
 __global__ void attn_combine_kernel(const AttnParams p, int HD) {
   pi_grid_dependency_wait();
@@ -275,6 +468,38 @@ cudaError_t launch_fast(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p) 
   }
 }
 
+template <int HD, int G, int STAGES>
+cudaError_t launch_tma_one(pi_ctx* ctx, dim3 grid, const AttnParams& p, size_t smem) {
+  auto k = attn_decode_tma_kernel<HD, G, STAGES>;
+  static size_t granted = 0;  // per instantiation: the attribute call is slow, so raise the limit only when needed
+  if (smem > granted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kAttnWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, k, p);
+}
+
+template <int HD, int STAGES>
+cudaError_t launch_tma(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p, size_t smem) {
+  switch (group) {
+    case 1: return launch_tma_one<HD, 1, STAGES>(ctx, grid, p, smem);
+    case 2: return launch_tma_one<HD, 2, STAGES>(ctx, grid, p, smem);
+    case 4: return launch_tma_one<HD, 4, STAGES>(ctx, grid, p, smem);
+    default: return launch_tma_one<HD, 8, STAGES>(ctx, grid, p, smem);
+  }
+}
+
 }  // namespace
 
 // Host block tables and per-entry metadata -> one device buffer, through pinned memory.
@@ -342,6 +567,7 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   p.pos = batch.pos;
   p.start = batch.start;
   p.scale = 1.0f / sqrtf((float)HD);
+  p.err_flag = ctx->dev_err;
   p.nsplit = 1;
   p.blocks_per_cta = std::max(batch.max_window_blocks, 1);
   p.part_ml = nullptr;
@@ -379,7 +605,14 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
     p.part_ml = p.part_acc + slots * HD;
   }
   const dim3 grid(L.num_kv_heads, batch.B, nsplit);
-  e = HD == 64 ? launch_fast<64>(ctx, group, grid, p) : launch_fast<128>(ctx, group, grid, p);
+  // Tiles staged through shared memory by bulk copies when a ring of them fits; direct loads otherwise.
+  const size_t tile_bytes = 2 * (size_t)L.block_size * HD * sizeof(float);
+  const int stages = HD == 64 ? 3 : 2;
+  const size_t ring_bytes = (size_t)kAttnWarps * stages * tile_bytes;
+  if (ctx->opt_attn_tma && tile_bytes % 16 == 0 && ring_bytes + 4096 <= ctx->smem_optin && tile_bytes < (1u << 20))
+    e = HD == 64 ? launch_tma<64, 3>(ctx, group, grid, p, ring_bytes) : launch_tma<128, 2>(ctx, group, grid, p, ring_bytes);
+  else
+    e = HD == 64 ? launch_fast<64>(ctx, group, grid, p) : launch_fast<128>(ctx, group, grid, p);
   if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
   ctx->launches++;
   if (nsplit > 1) {

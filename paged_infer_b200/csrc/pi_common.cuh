@@ -72,6 +72,7 @@ struct pi_ctx {
   bool opt_graph = true;
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
+  bool opt_attn_tma = true;
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
   bool prof_on = false;

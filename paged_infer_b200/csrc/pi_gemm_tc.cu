@@ -24,11 +24,15 @@
 //
 // Replaces math::matmat_i8_weight_parallel + transpose_rb_to_br for batches
 // beyond a few rows (reference src/math.rs:223-290).
+#include <cooperative_groups.h>
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <algorithm>
 
 #include "pi_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -53,6 +57,7 @@ struct GemmParams {
   size_t part_row_stride;   // N_pad
   size_t part_split_stride; // M_pad * N_pad
   int* err_flag;
+  int debug;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     uint32_t done;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -167,7 +172,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, kProducerWarps * 32 + 1);  // every producer thread + the TMA thread's expect_tx
+      mbar_init(full0 + 8 * s, kProducerWarps + 1);       // one arrival per producer warp + the TMA thread's expect_tx
       mbar_init(empty0 + 8 * s, 1);                        // one tcgen05.commit
     }
     mbar_init(accum_bar, 1);
@@ -186,8 +191,6 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   const uint32_t tmem = s_tmem;
   const uint32_t smem_base = smem_u32(smem);
 
-  pi_grid_dependency_wait();
-
   if (warp < kProducerWarps) {
     // ---- weight producers: 16 KiB of int8 per stage, 4 x 16 bytes per thread ----------------------
     // chunk c = i*256 + tid covers row c/8, bytes (c%8)*16..+16 of the stage's 128 K elements.
@@ -202,43 +205,68 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
       // 16 int8 -> 32 bytes of fp16 = chunks 2*(kc&3), 2*(kc&3)+1 of atom kc>>2, XOR-swizzled by the row
       dst[i] = (uint32_t)((kc >> 2) * (kBM * 128) + r * 128) | ((uint32_t)(r & 7) << 16) | ((uint32_t)(kc & 3) << 24);
     }
-    int4 cur[4], nxt[4];
-    if (kb_begin < kb_end) {
+    // Loads are issued a GROUP of kGroup K blocks at a time (512 contiguous bytes of every row), one group
+    // ahead of the one being widened: 64 KiB in flight per CTA hides the HBM latency, and asking for 512 bytes
+    // of a row at once - instead of 128 bytes now and the next 128 a microsecond later - is what keeps the DRAM
+    // pages open (a 2 KiB weight row is one page; 148 CTAs x 128 rows thrash the banks otherwise).
+    constexpr int kGroup = 4;
+    int4 cur[kGroup][4], nxt[kGroup][4];
+    auto load_group = [&](int4 (&g)[kGroup][4], int kb0) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) cur[i] = ld_stream_16(src[i] + (size_t)kb_begin * kBK);
+      for (int d = 0; d < kGroup; ++d)
+        if (kb0 + d < kb_end) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) g[d][i] = (p.debug & 1) ? make_int4(kb0, d, i, 1) : ld_stream_16(src[i] + (size_t)(kb0 + d) * kBK);
+        }
+    };
+    load_group(cur, kb_begin);
+    bool stop = false;
+    for (int kb0 = kb_begin; kb0 < kb_end && !stop; kb0 += kGroup) {
+      if (kb0 + kGroup < kb_end) load_group(nxt, kb0 + kGroup);
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d) {
+        const int kb = kb0 + d;
+        if (kb >= kb_end || stop) break;
+        const int it = kb - kb_begin, s = it % STAGES;
+        // lane 0 polls for the whole warp: 256 threads hammering one mbarrier cost more than the copy itself
+        int ok = 1;
+        if (lane == 0) ok = (!s_abort && mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0 && !s_abort) {
+            s_abort = 1;
+            if (p.err_flag) atomicExch(p.err_flag, 2);
+          }
+          stop = true;
+          break;
+        }
+        const uint32_t a_stage = smem_base + s * kStageBytes;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t h[8];
+          widen4((uint32_t)cur[d][i].x, h[0], h[1]);
+          widen4((uint32_t)cur[d][i].y, h[2], h[3]);
+          widen4((uint32_t)cur[d][i].z, h[4], h[5]);
+          widen4((uint32_t)cur[d][i].w, h[6], h[7]);
+          const uint32_t rowbase = a_stage + (dst[i] & 0xFFFF), sw = (dst[i] >> 16) & 7, c0 = ((dst[i] >> 24) & 3) * 2;
+          if (p.debug & 64) continue;
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + ((c0 ^ sw) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + (((c0 + 1) ^ sw) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+        }
+        if (!(p.debug & 32)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * s);
+      }
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cur[d][i] = nxt[d][i];
     }
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
-      const int it = kb - kb_begin, s = it % STAGES;
-      if (kb + 1 < kb_end) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) nxt[i] = ld_stream_16(src[i] + (size_t)(kb + 1) * kBK);
-      }
-      if (s_abort) break;
-      if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
-        s_abort = 1;
-        if (p.err_flag) atomicExch(p.err_flag, 2);
-        break;
-      }
-      const uint32_t a_stage = smem_base + s * kStageBytes;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t h[8];
-        widen4((uint32_t)cur[i].x, h[0], h[1]);
-        widen4((uint32_t)cur[i].y, h[2], h[3]);
-        widen4((uint32_t)cur[i].z, h[4], h[5]);
-        widen4((uint32_t)cur[i].w, h[6], h[7]);
-        const uint32_t rowbase = a_stage + (dst[i] & 0xFFFF), sw = (dst[i] >> 16) & 7, c0 = ((dst[i] >> 24) & 3) * 2;
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + ((c0 ^ sw) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + (((c0 + 1) ^ sw) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
-      mbar_arrive(full0 + 8 * s);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
-    }
+    pi_grid_dependency_wait();  // the epilogue below touches memory the producer kernel may still be writing
   } else if (warp == kProducerWarps) {
     // ---- activation loader: TMA, hi and lo planes, two 64-column boxes each ---------------------------
     if (lane == 0) {
+      pi_grid_dependency_wait();  // the activation planes come from the preceding kernel
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int it = kb - kb_begin, s = it % STAGES;
         if (s_abort) break;
@@ -249,6 +277,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
         }
         const uint32_t bar = full0 + 8 * s;
         const uint32_t b_stage = smem_base + s * kStageBytes + kATileBytes;
+        if (p.debug & 16) { mbar_arrive(bar); continue; }
         mbar_arrive_expect_tx(bar, 2 * kBTileBytes);
 #pragma unroll
         for (int plane = 0; plane < 2; ++plane) {
@@ -287,8 +316,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
             const uint64_t da = smem_desc(a_stage + atom * (kBM * 128) + ks * 32);
             const uint64_t dh = smem_desc(b_hi + atom * (BN * 128) + ks * 32);
             const uint64_t dl = smem_desc(b_lo + atom * (BN * 128) + ks * 32);
-            umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
-            umma_f16(tmem, da, dl, idesc, 1u);
+            if (!(p.debug & 2)) {
+              umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
+              umma_f16(tmem, da, dl, idesc, 1u);
+            }
           }
         }
         umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
@@ -300,11 +331,15 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   // ---- epilogue: warps 0-7 read the accumulator (warp w owns TMEM lanes 32*(w%4).., columns split in halves) ----
   bool have_acc = false;
   if (warp < kProducerWarps) {
-    have_acc = (kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0);
-    if (kb_begin < kb_end && !have_acc && !s_abort) {
-      s_abort = 1;
-      if (lane == 0 && p.err_flag) atomicExch(p.err_flag, 5);
+    int got = 0;
+    if (lane == 0) {
+      got = ((kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0)) ? 1 : 0;
+      if (kb_begin < kb_end && !got && !s_abort) {
+        s_abort = 1;
+        if (p.err_flag) atomicExch(p.err_flag, 5);
+      }
     }
+    have_acc = __shfl_sync(0xffffffffu, got, 0) != 0;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
   const int quad = warp & 3, half = warp >> 2;
@@ -312,7 +347,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
   const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
 
-  if (p.ksplit == 1) {
+  if (p.debug & 8) {
+  } else if (p.ksplit == 1) {
     if (epi_warp && have_acc) {
       const float ws = row < p.N ? p.scales[row] : 0.f;
 #pragma unroll 1
@@ -328,9 +364,13 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
       }
     }
   } else {
-    // write this split's raw partial sums, then let the last CTA of the tile add them in order
+    // K was split over the CTAs of a thread-block cluster (cluster rank = K slice).  Every CTA parks its raw
+    // partial tile in its own shared memory (the pipeline stages are free by now), the cluster synchronises,
+    // and each CTA then adds up and emits 1/ksplit of the tile's columns, reading its peers' tiles through
+    // distributed shared memory in rank order - so the sum does not depend on timing.
+    cg::cluster_group cluster = cg::this_cluster();
+    float* my_part = reinterpret_cast<float*>(smem);  // [BN][128]
     if (epi_warp) {
-      float* part = p.partial + (size_t)blockIdx.y * p.part_split_stride;
 #pragma unroll 1
       for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
         float v[16];
@@ -341,31 +381,43 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) part[(size_t)(m0 + c0 + j) * p.part_row_stride + row0 + quad * 32 + lane] = v[j];
+        for (int j = 0; j < 16; ++j) my_part[(c0 + j) * kBM + quad * 32 + lane] = v[j];
       }
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int idx = blockIdx.z * gridDim.x + blockIdx.x;
-      const int prev = atomicAdd(&p.counters[idx], 1);
-      s_last = (prev == p.ksplit - 1);
-      if (s_last) p.counters[idx] = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (s_last && epi_warp) {
-      __threadfence();
-      const float ws = row < p.N ? p.scales[row] : 0.f;
-#pragma unroll 1
-      for (int c = half * kColsPerHalf; c < (half + 1) * kColsPerHalf && c < BN; ++c) {
-        const int m = m0 + c;
-        float acc = 0.f;
-        for (int ks = 0; ks < p.ksplit; ++ks)
-          acc += __ldcg(p.partial + (size_t)ks * p.part_split_stride + (size_t)m * p.part_row_stride + row0 + quad * 32 + lane);
-        const float as = m < p.M ? p.act_scale[m] : 0.f;
-        emit(p, m, row, acc * ws * as, lane);
+    cluster.sync();
+    const int rank = (int)cluster.block_rank(), nranks = p.ksplit;
+    // this CTA's columns: rank, rank + nranks, ...; 32 threads x float4 cover the 128 rows of a column
+    if (tid < kProducerWarps * 32) {
+      const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 8 columns in flight per pass
+      for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < nranks; ++r) {
+          const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int m = m0 + c, rr = row0 + r4;
+        if (m < p.M && rr < p.N) {
+          const float as = p.act_scale[m];
+          const float v0 = acc.x * p.scales[rr] * as;
+          const float v1 = rr + 1 < p.N ? acc.y * p.scales[rr + 1] * as : 0.f;
+          const float v2 = rr + 2 < p.N ? acc.z * p.scales[rr + 2] * as : 0.f;
+          const float v3 = rr + 3 < p.N ? acc.w * p.scales[rr + 3] * as : 0.f;
+          if (p.epi == PI_EPI_SWIGLU) {
+            float* o = p.out + (size_t)m * p.out_stride + (rr >> 1);
+            if (rr + 1 < p.N) o[0] = silu_mul(v0, v1);
+            if (rr + 3 < p.N) o[1] = silu_mul(v2, v3);
+          } else {
+            float* o = p.out + (size_t)m * p.out_stride + rr;
+            const bool add = p.epi == PI_EPI_ADD;
+            o[0] = add ? o[0] + v0 : v0;
+            if (rr + 1 < p.N) o[1] = add ? o[1] + v1 : v1;
+            if (rr + 2 < p.N) o[2] = add ? o[2] + v2 : v2;
+            if (rr + 3 < p.N) o[3] = add ? o[3] + v3 : v3;
+          }
+        }
       }
     }
+    cluster.sync();  // nobody leaves while a peer may still be reading its tile
   }
   pi_grid_launch_dependents();
 
@@ -455,18 +507,33 @@ template <int BN, int STAGES>
 cudaError_t launch_tc(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& hi, const CUtensorMap& lo, dim3 grid) {
   constexpr size_t smem = (size_t)STAGES * (kATileBytes + 4 * BN * 128) + 1024;
   auto k = gemm_tc_kernel<BN, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
+  static bool granted = false;  // per instantiation
+  if (!granted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted = true;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (ctx->opt_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (grid.y > 1) {  // the K slices of one row tile form a cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = grid.y;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, k, p, hi, lo);
 }
 
@@ -494,8 +561,8 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   int ksplit = 1;
   const int tiles = rtiles * mtiles;
   if (tiles < ctx->sm_count) {
-    ksplit = std::min(std::max(1, (ctx->sm_count * 3 / 2) / tiles), std::max(1, nkb / 2));
-    ksplit = std::min(ksplit, 32);
+    const int want = std::min(std::max(1, (ctx->sm_count * 3 / 2) / tiles), std::max(1, nkb / 2));
+    while (ksplit * 2 <= want && ksplit < 8) ksplit *= 2;   // a portable cluster holds up to 8 CTAs
   }
 
   // workspace: [act hi | act lo | act_scale] and [counters | partials]
@@ -513,7 +580,8 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   }
 
   pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
-  {
+  const char* dbg_env = getenv("PI_GEMM_DEBUG");
+  if (!(dbg_env && (atoi(dbg_env) & 4))) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(M);
     cfg.blockDim = dim3(256);
@@ -524,8 +592,11 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
-    if (cfg.dynamicSmemBytes > 48 * 1024)
+    static size_t split_granted = 48 * 1024;
+    if (cfg.dynamicSmemBytes > split_granted) {
       PI_CUDA(ctx, cudaFuncSetAttribute(act_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes));
+      split_granted = cfg.dynamicSmemBytes;
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, act_split_kernel, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
     if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
     ctx->launches++;
@@ -561,6 +632,7 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   p.part_row_stride = N_pad;
   p.part_split_stride = (size_t)M_pad * N_pad;
   p.err_flag = ctx->dev_err;
+  { const char* dbg = getenv("PI_GEMM_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
   const dim3 grid(rtiles, ksplit, mtiles);
   cudaError_t e;
   switch (BN) {

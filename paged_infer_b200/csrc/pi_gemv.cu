@@ -120,10 +120,21 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     const int row = min(row0 + r, p.N - 1);
     wrow[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * ld * sizeof(WT);
   }
-  int k0 = lane * EPL;
-  int4 wv[kRows];
+  // Weight loads go out a GROUP of kSteps steps at a time (kSteps * 512 bytes of each row in one burst), one
+  // group ahead of the arithmetic: enough bytes in flight to cover the HBM latency, and whole DRAM pages per visit.
+  constexpr int kSteps = 4;
+  constexpr int kStepElems = 32 * EPL;
+  const int k_lane = lane * EPL;
+  int4 wcur[kSteps][kRows], wnxt[kSteps][kRows];
+  auto load_group = [&](int4 (&g)[kSteps][kRows], int kbase) {
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) wv[r] = (k0 < ld) ? ld_stream_16(wrow[r] + (size_t)k0 * sizeof(WT)) : make_int4(0, 0, 0, 0);
+    for (int t = 0; t < kSteps; ++t) {
+      const int k = kbase + t * kStepElems + k_lane;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) g[t][r] = (k < ld) ? ld_stream_16(wrow[r] + (size_t)k * sizeof(WT)) : make_int4(0, 0, 0, 0);
+    }
+  };
+  load_group(wcur, 0);
 
   pi_grid_dependency_wait();
 
@@ -235,32 +246,37 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
 
   const int s = unit_swizzle<U>(lane);
-  for (; k0 < ld; k0 += 32 * EPL) {
-    const int kn = k0 + 32 * EPL;
-    int4 wn[kRows];
+  for (int kbase = 0; kbase < ld; kbase += kSteps * kStepElems) {
+    if (kbase + kSteps * kStepElems < ld) load_group(wnxt, kbase + kSteps * kStepElems);
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) wn[r] = (kn < ld) ? ld_stream_16(wrow[r] + (size_t)kn * sizeof(WT)) : make_int4(0, 0, 0, 0);
-
-    float wf[kRows][EPL];
+    for (int t = 0; t < kSteps; ++t) {
+      const int k0 = kbase + t * kStepElems + k_lane;
+      if (kbase + t * kStepElems >= ld) break;   // uniform across the warp
+      if (k0 < ld) {
+        float wf[kRows][EPL];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) Widen<WT>::run(wv[r], wf[r]);
+        for (int r = 0; r < kRows; ++r) Widen<WT>::run(wcur[t][r], wf[r]);
 #pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      const float4* xb = reinterpret_cast<const float4*>(xs + (size_t)m * ld + k0);
+        for (int m = 0; m < MB; ++m) {
+          const float4* xb = reinterpret_cast<const float4*>(xs + (size_t)m * ld + k0);
 #pragma unroll
-      for (int j = 0; j < U; ++j) {
-        const float4 xv = xb[j ^ s];
+          for (int j = 0; j < U; ++j) {
+            const float4 xv = xb[j ^ s];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-          acc[r][m] = fmaf(wf[r][4 * j + 0], xv.x, acc[r][m]);
-          acc[r][m] = fmaf(wf[r][4 * j + 1], xv.y, acc[r][m]);
-          acc[r][m] = fmaf(wf[r][4 * j + 2], xv.z, acc[r][m]);
-          acc[r][m] = fmaf(wf[r][4 * j + 3], xv.w, acc[r][m]);
+            for (int r = 0; r < kRows; ++r) {
+              acc[r][m] = fmaf(wf[r][4 * j + 0], xv.x, acc[r][m]);
+              acc[r][m] = fmaf(wf[r][4 * j + 1], xv.y, acc[r][m]);
+              acc[r][m] = fmaf(wf[r][4 * j + 2], xv.z, acc[r][m]);
+              acc[r][m] = fmaf(wf[r][4 * j + 3], xv.w, acc[r][m]);
+            }
+          }
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) wv[r] = wn[r];
+    for (int t = 0; t < kSteps; ++t)
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) wcur[t][r] = wnxt[t][r];
   }
 
 #pragma unroll
@@ -308,9 +324,16 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
     if (norm) PI_PICK(PI_EPI_SWIGLU, true); else PI_PICK(PI_EPI_SWIGLU, false);
   }
 #undef PI_PICK
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+  static size_t granted = 48 * 1024;  // per instantiation of this launcher; attribute calls are slow
+  if (smem > granted) {
+    // the launcher covers several kernel variants: raise the limit on all of them at once
+    for (auto kk : {gemv_kernel<WT, MB, PI_EPI_STORE, true>, gemv_kernel<WT, MB, PI_EPI_STORE, false>,
+                    gemv_kernel<WT, MB, PI_EPI_ADD, true>, gemv_kernel<WT, MB, PI_EPI_ADD, false>,
+                    gemv_kernel<WT, MB, PI_EPI_SWIGLU, true>, gemv_kernel<WT, MB, PI_EPI_SWIGLU, false>}) {
+      cudaError_t e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    granted = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

@@ -551,17 +551,41 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
 }
 
 // After a greedy step: the chosen ids become the next inputs, every sequence moves on one position.
-static __global__ void advance_kernel(uint32_t* tokens, const uint32_t* chosen, uint32_t* history, int32_t* pos,
-                                      int32_t* start, int window, int B) {
+// The step index lives on the device so that one captured graph serves every step.
+static __global__ void advance_kernel(uint32_t* tokens, const uint32_t* chosen, uint32_t* history, int* step_counter,
+                                      int32_t* pos, int32_t* start, int window, int B) {
   pi_grid_dependency_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= B) return;
-  const uint32_t t = chosen[b];
-  tokens[b] = t;
-  history[b] = t;
-  const int p = pos[b] + 1;
-  pos[b] = p;
-  start[b] = window < 0 ? 0 : max(0, p + 1 - window);
+  const int step = *step_counter;
+  if (b < B) {
+    const uint32_t t = chosen[b];
+    tokens[b] = t;
+    history[(size_t)step * B + b] = t;
+    const int p = pos[b] + 1;
+    pos[b] = p;
+    start[b] = window < 0 ? 0 : max(0, p + 1 - window);
+  }
+}
+
+// Bumps the step counter once all blocks of advance_kernel are done (stream order).
+static __global__ void next_step_kernel(int* step_counter) {
+  pi_grid_dependency_wait();
+  step_counter[0] += 1;
+}
+
+static pi_status decode_one_step(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_batch& batch, int B,
+                                 uint32_t* history, int* step_counter) {
+  PI_TRY(run_layers(ctx, m, pool, batch, B));
+  PI_TRY(project_logits(ctx, m, 0, B));
+  PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
+  pi_prof_scope prof(ctx, PI_PROF_OTHER);
+  advance_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(m->tokens_dev, m->argmax_dev, history, step_counter,
+                                                           const_cast<int32_t*>(batch.pos), const_cast<int32_t*>(batch.start),
+                                                           m->cfg.attention_window, B);
+  PI_CHECK_LAUNCH(ctx);
+  next_step_kernel<<<1, 1, 0, ctx->stream>>>(step_counter);
+  PI_CHECK_LAUNCH(ctx);
+  return PI_OK;
 }
 
 pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host,
@@ -577,24 +601,49 @@ pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
   int max_pos = 0;
   for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, positions_host[b]);
   PI_TRY(ensure_rope(ctx, m, max_pos + n_steps));
-  PI_TRY(pi_reserve(ctx, &ctx->staging_out, (size_t)n_steps * B * sizeof(uint32_t)));
-  uint32_t* history = static_cast<uint32_t*>(ctx->staging_out.ptr);
+  PI_TRY(pi_reserve(ctx, &ctx->staging_out, 64 + (size_t)n_steps * B * sizeof(uint32_t)));
+  int* step_counter = static_cast<int*>(ctx->staging_out.ptr);
+  uint32_t* history = reinterpret_cast<uint32_t*>(static_cast<char*>(ctx->staging_out.ptr) + 64);
+  PI_CUDA(ctx, cudaMemsetAsync(step_counter, 0, 64, ctx->stream));
   pi_attn_batch batch;
   PI_TRY(stage_batch(ctx, m, pool, tokens_host, positions_host, block_tables_host, max_blocks, table_lens_host, B, &batch));
   // The KV split is planned on the host from the final positions, so that every step fits it.
   const int bs = pool->L.block_size;
   batch.total_window_blocks += (long)B * ((n_steps + bs - 1) / bs);
   batch.max_window_blocks += (n_steps + bs - 1) / bs;
-  for (int s = 0; s < n_steps; ++s) {
-    PI_TRY(run_layers(ctx, m, pool, batch, B));
-    PI_TRY(project_logits(ctx, m, 0, B));
-    PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
-    pi_prof_scope prof(ctx, PI_PROF_OTHER);
-    advance_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(m->tokens_dev, m->argmax_dev, history + (size_t)s * B,
-                                                             const_cast<int32_t*>(batch.pos),
-                                                             const_cast<int32_t*>(batch.start), m->cfg.attention_window, B);
-    PI_CHECK_LAUNCH(ctx);
+
+  // Step 0 runs eagerly (it also sizes every scratch buffer).  The remaining steps are identical launches
+  // over device-resident state, so one step is captured into a CUDA graph and replayed.
+  PI_TRY(decode_one_step(ctx, m, pool, batch, B, history, step_counter));
+  int done = 1;
+  if (ctx->opt_graph && !ctx->prof_on && n_steps >= 4) {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    const uint64_t before = ctx->launches;
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      pi_status st = decode_one_step(ctx, m, pool, batch, B, history, step_counter);
+      e = cudaStreamEndCapture(ctx->stream, &graph);
+      const uint64_t per_step = ctx->launches - before;
+      ctx->launches = before;
+      if (st == PI_OK && e == cudaSuccess && graph) e = cudaGraphInstantiate(&exec, graph, 0);
+      if (st == PI_OK && e == cudaSuccess && exec) {
+        for (; done < n_steps; ++done) {
+          e = cudaGraphLaunch(exec, ctx->stream);
+          if (e != cudaSuccess) break;
+          ctx->launches += per_step;
+        }
+      }
+      if (exec) cudaGraphExecDestroy(exec);
+      if (graph) cudaGraphDestroy(graph);
+      if (st != PI_OK) return st;
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();  // fall back to eager launches for whatever is left
+      ctx->err = std::string("CUDA graph path unavailable: ") + cudaGetErrorString(e);
+    }
   }
+  for (; done < n_steps; ++done) PI_TRY(decode_one_step(ctx, m, pool, batch, B, history, step_counter));
   PI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, history, (size_t)n_steps * B * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
   return pi_ctx_synchronize(ctx);
 }

@@ -274,3 +274,30 @@ def test_batch_64_ragged_decode_with_shared_prefix_blocks(ctx, oracle):
         mism += sum(int(a != b) for a, b in zip(ids.tolist(), wa))
         nxt, pos = wa, [p + 1 for p in pos]
     assert worst < 1e-3 and mism == 0, (worst, mism)
+
+
+def test_multi_step_decode_equals_step_by_step(ctx, oracle):
+    """n greedy steps in one call (eager first step, then a replayed CUDA graph) == n single-step calls."""
+    from paged_infer_b200 import api
+    cfg, om, gm = small_llama(ctx, oracle, 5)
+    rng = np.random.default_rng(5)
+    for B, n in ((1, 9), (7, 6), (40, 5), (3, 2)):
+        lens = [int(x) for x in rng.integers(3, 60, B)]
+        tables = [[b * 6 + i for i in range(6)] for b in range(B)]
+        kv_a = api.KvCache(ctx, gm.kv_layout(6 * B, BLOCK))
+        kv_b = api.KvCache(ctx, gm.kv_layout(6 * B, BLOCK))
+        zero = np.zeros(kv_floats(cfg, 6 * B), np.float32)
+        kv_a.upload(zero)
+        kv_b.upload(zero)
+        for b in range(B):
+            prompt = rng.integers(0, cfg.vocab_size, lens[b]).astype(np.uint32)
+            gm.prefill_batched(prompt, 0, tables[b], kv_a, 16)
+            gm.prefill_batched(prompt, 0, tables[b], kv_b, 16)
+        tok = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
+        multi = gm.decode_multi(tok, lens, tables, kv_a, n)
+        cur, pos = tok, list(lens)
+        for s in range(n):
+            cur = gm.decode_batch_into(cur, pos, tables, kv_b, want_logits=False, want_argmax=True)
+            assert multi[s].tolist() == cur.tolist(), (B, s)
+            pos = [p + 1 for p in pos]
+        assert np.abs(kv_a.download() - kv_b.download()).max() < 1e-5
