@@ -72,7 +72,7 @@ struct pi_ctx {
   bool opt_graph = true;
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
-  bool opt_attn_tma = true;
+  int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
   bool prof_on = false;
