@@ -2,21 +2,30 @@
 //
 // y[m][r] = scale[r] * sum_k W[r][k] * x[m][k] with W int8 (or bf16 / f32 with
 // scale 1), x f32, f32 accumulation.  This is the decode-sized path: every
-// weight byte is read from HBM exactly once per launch with 128-bit loads, the
-// activations are staged into shared memory once per CTA by a bulk async copy
-// (TMA, cp.async.bulk) and read back conflict-free, each warp owns two output
-// rows and reduces with shuffles.  Optional fusions: an RMSNorm prologue on x,
-// and residual-add or SwiGLU epilogues.
+// weight byte is read from HBM exactly once per launch with 128-bit loads.
+//
+// The grid is persistent (a couple of CTAs per SM).  Each CTA stages the
+// activations into shared memory once with a bulk async copy (TMA,
+// cp.async.bulk), optionally applies RMSNorm to them there, and stores them in a
+// layout that makes the later 128-bit reads conflict-free.  Each warp then walks
+// row pairs; its weight loads are issued a group of 4 steps (2 KiB per row) at a
+// time and one group ahead of the arithmetic, so that enough bytes are in flight
+// to cover the HBM latency and a DRAM page is visited once.  int8 is widened
+// with a byte permute into the mantissa of 2^23 (no quarter-rate I2F); products
+// use packed fma.rn.f32x2; rows are reduced with shuffles.  Epilogues: store,
+// residual add, or SwiGLU over interleaved gate/up rows.
 //
 // Replaces math::matvec_i8_weight_parallel / matmat_i8_weight_parallel and the
 // f32 twins (reference src/math.rs:93-275, :473-512) and math::quantize_rows_i8
 // (:456-469).
+#include <algorithm>
+
 #include "pi_common.cuh"
 
 namespace {
 
-constexpr int kRows = 2;       // output rows per warp
-constexpr int kMaxMB = 4;      // activation rows per CTA pass
+constexpr int kRows = 2;    // output rows per warp pass
+constexpr int kSteps = 4;   // 512-byte steps of a row per load group
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -29,7 +38,7 @@ __device__ __forceinline__ int4 ld_stream_16(const void* p) {
   return v;
 }
 
-// 16 bytes of weights -> EPL floats.
+// 16 bytes of weights -> EPL floats, as float2 pairs.
 template <typename WT>
 struct Widen;
 template <>
@@ -37,38 +46,36 @@ struct Widen<int8_t> {
   static constexpr int EPL = 16;
   // int8 -> f32 without the quarter-rate I2F: flip the sign bit so the byte is
   // b+128 in [0,255], drop it into the mantissa of 2^23, subtract 2^23+128.
-  __device__ static __forceinline__ void run(const int4& v, float* f) {
+  __device__ static __forceinline__ void run(const int4& v, float2* f) {
     const uint32_t w[4] = {(uint32_t)v.x ^ 0x80808080u, (uint32_t)v.y ^ 0x80808080u, (uint32_t)v.z ^ 0x80808080u,
                            (uint32_t)v.w ^ 0x80808080u};
+    const float2 bias = make_float2(-8388736.0f, -8388736.0f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      f[4 * i + 0] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.0f;
-      f[4 * i + 1] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.0f;
-      f[4 * i + 2] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.0f;
-      f[4 * i + 3] = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)) - 8388736.0f;
+      const float2 a = make_float2(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)),
+                                   __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)));
+      const float2 b = make_float2(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)),
+                                   __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)));
+      f[2 * i + 0] = __fadd2_rn(a, bias);
+      f[2 * i + 1] = __fadd2_rn(b, bias);
     }
   }
 };
 template <>
 struct Widen<uint16_t> {  // bf16 bits
   static constexpr int EPL = 8;
-  __device__ static __forceinline__ void run(const int4& v, float* f) {
+  __device__ static __forceinline__ void run(const int4& v, float2* f) {
     const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[2 * i + 0] = __uint_as_float(w[i] << 16);
-      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
+    for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
   }
 };
 template <>
 struct Widen<float> {
   static constexpr int EPL = 4;
-  __device__ static __forceinline__ void run(const int4& v, float* f) {
-    f[0] = __int_as_float(v.x);
-    f[1] = __int_as_float(v.y);
-    f[2] = __int_as_float(v.z);
-    f[3] = __int_as_float(v.w);
+  __device__ static __forceinline__ void run(const int4& v, float2* f) {
+    f[0] = make_float2(__int_as_float(v.x), __int_as_float(v.y));
+    f[1] = make_float2(__int_as_float(v.z), __int_as_float(v.w));
   }
 };
 
@@ -100,6 +107,8 @@ template <typename WT, int MB, int EPI, bool NORM>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   constexpr int EPL = Widen<WT>::EPL;
   constexpr int U = EPL / 4;
+  constexpr int kStepElems = 32 * EPL;
+  constexpr int kGroupElems = kSteps * kStepElems;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);  // [MB][ld]
   __shared__ __align__(8) unsigned long long mbar;
@@ -110,35 +119,32 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   const int ld = (int)p.ld, K = p.K;
   const int m0 = blockIdx.y * MB;
   const int mcount = min(MB, p.M - m0);
-
-  // Weight rows of this warp; the first 16-byte chunks are requested before the
-  // activations are waited for, since they do not depend on the producer kernel.
-  const int row0 = (blockIdx.x * nwarps + warp) * kRows;
-  const unsigned char* wrow[kRows];
-#pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    const int row = min(row0 + r, p.N - 1);
-    wrow[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * ld * sizeof(WT);
-  }
-  // Weight loads go out a GROUP of kSteps steps at a time (kSteps * 512 bytes of each row in one burst), one
-  // group ahead of the arithmetic: enough bytes in flight to cover the HBM latency, and whole DRAM pages per visit.
-  constexpr int kSteps = 4;
-  constexpr int kStepElems = 32 * EPL;
+  const int npairs = (p.N + kRows - 1) / kRows;
+  const int ngroups = (ld + kGroupElems - 1) / kGroupElems;
+  const int total_warps = gridDim.x * nwarps;
   const int k_lane = lane * EPL;
+
+  // Work items of this warp: (row pair, K group), row pairs strided by the number of warps in the grid.
   int4 wcur[kSteps][kRows], wnxt[kSteps][kRows];
-  auto load_group = [&](int4 (&g)[kSteps][kRows], int kbase) {
+  auto load_group = [&](int4 (&g)[kSteps][kRows], int pair, int kg) {
+    const unsigned char* rowp[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      rowp[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)min(pair * kRows + r, p.N - 1) * ld * sizeof(WT);
 #pragma unroll
     for (int t = 0; t < kSteps; ++t) {
-      const int k = kbase + t * kStepElems + k_lane;
+      const int k = kg * kGroupElems + t * kStepElems + k_lane;
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) g[t][r] = (k < ld) ? ld_stream_16(wrow[r] + (size_t)k * sizeof(WT)) : make_int4(0, 0, 0, 0);
+      for (int r = 0; r < kRows; ++r) g[t][r] = (k < ld) ? ld_stream_16(rowp[r] + (size_t)k * sizeof(WT)) : make_int4(0, 0, 0, 0);
     }
   };
-  load_group(wcur, 0);
+  int pair = blockIdx.x * nwarps + warp, kg = 0;
+  // the first group does not depend on the producer kernel: request it before waiting for the activations
+  if (pair < npairs) load_group(wcur, pair, 0);
 
   pi_grid_dependency_wait();
 
-  // ---- stage x[m0 .. m0+mcount) into shared memory --------------------------
+  // ---- stage x[m0 .. m0+mcount) into shared memory, once per CTA ---------------------------------
   bool landed = false;
   if (p.use_tma) {
     if (tid == 0) {
@@ -239,21 +245,28 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   pi_grid_launch_dependents();
 
   // ---- stream the weight rows -------------------------------------------------
-  float acc[kRows][MB];
+  float2 acc[kRows][MB];  // even / odd partial sums
 #pragma unroll
   for (int r = 0; r < kRows; ++r)
 #pragma unroll
-    for (int m = 0; m < MB; ++m) acc[r][m] = 0.f;
+    for (int m = 0; m < MB; ++m) acc[r][m] = make_float2(0.f, 0.f);
 
   const int s = unit_swizzle<U>(lane);
-  for (int kbase = 0; kbase < ld; kbase += kSteps * kStepElems) {
-    if (kbase + kSteps * kStepElems < ld) load_group(wnxt, kbase + kSteps * kStepElems);
+  while (pair < npairs) {
+    int npair = pair, nkg = kg + 1;
+    if (nkg == ngroups) {
+      nkg = 0;
+      npair = pair + total_warps;
+    }
+    if (npair < npairs) load_group(wnxt, npair, nkg);
+
+    const int kbase = kg * kGroupElems;
 #pragma unroll
     for (int t = 0; t < kSteps; ++t) {
+      if (kbase + t * kStepElems >= ld) break;  // uniform across the warp
       const int k0 = kbase + t * kStepElems + k_lane;
-      if (kbase + t * kStepElems >= ld) break;   // uniform across the warp
       if (k0 < ld) {
-        float wf[kRows][EPL];
+        float2 wf[kRows][EPL / 2];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) Widen<WT>::run(wcur[t][r], wf[r]);
 #pragma unroll
@@ -262,52 +275,57 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
           for (int j = 0; j < U; ++j) {
             const float4 xv = xb[j ^ s];
+            const float2 xlo = make_float2(xv.x, xv.y), xhi = make_float2(xv.z, xv.w);
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
-              acc[r][m] = fmaf(wf[r][4 * j + 0], xv.x, acc[r][m]);
-              acc[r][m] = fmaf(wf[r][4 * j + 1], xv.y, acc[r][m]);
-              acc[r][m] = fmaf(wf[r][4 * j + 2], xv.z, acc[r][m]);
-              acc[r][m] = fmaf(wf[r][4 * j + 3], xv.w, acc[r][m]);
+              acc[r][m] = __ffma2_rn(wf[r][2 * j + 0], xlo, acc[r][m]);
+              acc[r][m] = __ffma2_rn(wf[r][2 * j + 1], xhi, acc[r][m]);
             }
           }
         }
+      }
+    }
+
+    if (kg == ngroups - 1) {  // the row pair is complete: reduce, apply the scale, write
+      const int row0 = pair * kRows;
+      float tot[kRows][MB];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          tot[r][m] = pi_warp_sum(acc[r][m].x + acc[r][m].y);
+          acc[r][m] = make_float2(0.f, 0.f);
+        }
+      float sc[kRows];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) sc[r] = (p.scales && row0 + r < p.N) ? p.scales[row0 + r] : 1.0f;
+      if (EPI == PI_EPI_SWIGLU) {
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          if (lane == m && m < mcount && row0 + 1 < p.N) {
+            const float g = tot[0][m] * sc[0], u = tot[1][m] * sc[1];
+            p.out[(size_t)(m0 + m) * p.out_stride + (row0 >> 1)] = (g / (1.0f + expf(-g))) * u;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+#pragma unroll
+          for (int m = 0; m < MB; ++m) {
+            if (lane == r * MB + m && m < mcount && row0 + r < p.N) {
+              float* o = p.out + (size_t)(m0 + m) * p.out_stride + row0 + r;
+              const float v = tot[r][m] * sc[r];
+              *o = (EPI == PI_EPI_ADD) ? (*o + v) : v;
+            }
+          }
       }
     }
 #pragma unroll
     for (int t = 0; t < kSteps; ++t)
 #pragma unroll
       for (int r = 0; r < kRows; ++r) wcur[t][r] = wnxt[t][r];
-  }
-
-#pragma unroll
-  for (int r = 0; r < kRows; ++r)
-#pragma unroll
-    for (int m = 0; m < MB; ++m) acc[r][m] = pi_warp_sum(acc[r][m]);
-
-  // ---- epilogue ------------------------------------------------------------------
-  if (row0 >= p.N) return;
-  float sc[kRows];
-#pragma unroll
-  for (int r = 0; r < kRows; ++r) sc[r] = (p.scales && row0 + r < p.N) ? p.scales[row0 + r] : 1.0f;
-  if (EPI == PI_EPI_SWIGLU) {
-#pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      if (lane == m && m < mcount) {
-        const float g = acc[0][m] * sc[0], u = acc[1][m] * sc[1];
-        p.out[(size_t)(m0 + m) * p.out_stride + (row0 >> 1)] = (g / (1.0f + expf(-g))) * u;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int r = 0; r < kRows; ++r)
-#pragma unroll
-      for (int m = 0; m < MB; ++m) {
-        if (lane == r * MB + m && m < mcount && row0 + r < p.N) {
-          float* o = p.out + (size_t)(m0 + m) * p.out_stride + row0 + r;
-          const float v = acc[r][m] * sc[r];
-          *o = (EPI == PI_EPI_ADD) ? (*o + v) : v;
-        }
-      }
+    pair = npair;
+    kg = nkg;
   }
 }
 
@@ -406,17 +424,20 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
   PI_REQUIRE(ctx, a.M >= 1, "projection batch must be at least 1");
   PI_REQUIRE(ctx, a.epi != PI_EPI_SWIGLU || lin->rows % 2 == 0, "SwiGLU epilogue needs interleaved gate/up rows");
   if (lin->rows == 0) return PI_OK;
-  const size_t esz = lin->kind == PI_INT8 ? 1 : lin->kind == PI_BF16 ? 2 : 4;
-  (void)esz;
   int mb = a.M >= 4 ? 4 : a.M >= 2 ? 2 : 1;
   while (mb > 1 && (size_t)mb * lin->ld * sizeof(float) > ctx->smem_optin - 2048) mb >>= 1;
   const size_t smem = (size_t)mb * lin->ld * sizeof(float);
   PI_REQUIRE(ctx, smem <= ctx->smem_optin - 2048, "projection input of %zu columns does not fit shared memory", lin->cols);
 
-  // Enough CTAs to cover the SMs a few times over; wide CTAs only for tall matrices.
+  // Persistent grid: two CTAs of up to 8 warps per SM; narrower CTAs when there are few row pairs, so that
+  // every SM still gets work.
+  const size_t npairs = (lin->rows + kRows - 1) / kRows;
+  const int mtiles = (a.M + mb - 1) / mb;
+  const size_t max_ctas = std::max<size_t>(1, (size_t)ctx->sm_count * 2 / mtiles);
   int warps = 8;
-  while (warps > 2 && (lin->rows + (size_t)warps * kRows - 1) / ((size_t)warps * kRows) < (size_t)ctx->sm_count * 2) warps >>= 1;
-  dim3 grid((unsigned)((lin->rows + (size_t)warps * kRows - 1) / ((size_t)warps * kRows)), (unsigned)((a.M + mb - 1) / mb));
+  while (warps > 1 && (npairs + warps - 1) / warps < max_ctas) warps >>= 1;
+  const size_t ctas = std::min<size_t>((npairs + warps - 1) / warps, max_ctas);
+  dim3 grid((unsigned)ctas, (unsigned)mtiles);
 
   GemvParams p;
   p.W = lin->w;
