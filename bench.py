@@ -251,11 +251,16 @@ def gemv_sweep(api, ctx, torch, hbm_peak, reps=3):
         torch.cuda.synchronize()
         best = None
         for _ in range(reps):
-            ctx.profile_begin()           # CUDA events around every launch, on the launching stream
-            for l in lins:
-                l.apply_device(x, y, 1)
-            ms, n = ctx.profile_end()["gemv"]
-            us = ms * 1e3 / max(n, 1)
+            # back-to-back launches over the rotating copies, one CUDA-event pair around the whole train on the
+            # launching stream: per-launch = total / launches (a pair of events per launch would add ~4 us each)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _r in range(4):
+                for l in lins:
+                    l.apply_device(x, y, 1)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (4 * copies)
             best = us if best is None else min(best, us)
         algo = N * K + 4 * N + 4 * K + 4 * N
         out[name] = {"us": round(best, 3), "GB/s": round(algo / best / 1e3, 1), "frac_of_hbm_peak": round(algo / best / 1e3 / hbm_peak, 3),

@@ -222,6 +222,13 @@ __device__ __forceinline__ float pi_warp_max(float v) {
 __device__ __forceinline__ float pi_bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
 // Programmatic dependent launch: wait for the producer grid's memory, and allow
 // the consumer grid to start its prologue.
-__device__ __forceinline__ void pi_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Every kernel of this library guards its first dependent access with this call, so the next kernel in
+// the stream may be released right here: it can then run its own independent prologue (barrier set-up, TMEM
+// allocation, weight prefetch) while this grid is still working, and blocks in its own wait until this grid has
+// completed.  The dependent grid is only released once every CTA of this grid has passed this point or exited.
+__device__ __forceinline__ void pi_grid_dependency_wait() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void pi_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif

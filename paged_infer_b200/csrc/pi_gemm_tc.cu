@@ -19,8 +19,9 @@
 // word instead of hanging.
 //
 // K is split across CTAs when there are too few row tiles to fill the SMs; the
-// last CTA to finish a tile adds the partial sums in a fixed order, so results
-// do not depend on timing.
+// K slices of one row tile form a thread-block cluster and add their partial
+// tiles through distributed shared memory in rank order, so results do not
+// depend on timing.
 //
 // Replaces math::matmat_i8_weight_parallel + transpose_rb_to_br for batches
 // beyond a few rows (reference src/math.rs:223-290).
@@ -52,12 +53,7 @@ struct GemmParams {
   int N, K, M;
   int ksplit, nkb;          // K splits, total K blocks
   int epi;
-  float* partial;           // [ksplit][M_pad][N_pad] when ksplit > 1
-  int* counters;            // one per (row tile, batch tile)
-  size_t part_row_stride;   // N_pad
-  size_t part_split_stride; // M_pad * N_pad
   int* err_flag;
-  int debug;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -163,12 +159,42 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
   __shared__ uint32_t s_tmem;
   __shared__ volatile int s_abort;
-  __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
   const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+
+  // ---- weight producers (warps 0-7): 16 KiB of int8 per stage, 4 x 16 bytes per thread ----------------------
+  // chunk c = i*256 + tid covers row c/8, bytes (c%8)*16..+16 of the stage's 128 K elements.
+  // Loads are issued a GROUP of kGroup K blocks at a time (512 contiguous bytes of every row), one group ahead
+  // of the one being widened: 64 KiB in flight per CTA.  The first group is requested before anything else in
+  // the kernel - weights never depend on the preceding kernel - so barrier set-up and the TMEM allocation hide
+  // behind its latency.
+  constexpr int kGroup = 4;
+  const unsigned char* src[4];
+  uint32_t dst[4];
+  int4 cur[kGroup][4], nxt[kGroup][4];
+  auto load_group = [&](int4 (&g)[kGroup][4], int kb0) {
+#pragma unroll
+    for (int d = 0; d < kGroup; ++d)
+      if (kb0 + d < kb_end) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) g[d][i] = ld_stream_16(src[i] + (size_t)(kb0 + d) * kBK);
+      }
+  };
+  if (warp < kProducerWarps) {
+    const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.W);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = i * 256 + tid, r = c >> 3, kc = c & 7;
+      const int row = min(row0 + r, p.N - 1);
+      src[i] = wbase + (size_t)row * p.ld + kc * 16;
+      // 16 int8 -> 32 bytes of fp16 = chunks 2*(kc&3), 2*(kc&3)+1 of atom kc>>2, XOR-swizzled by the row
+      dst[i] = (uint32_t)((kc >> 2) * (kBM * 128) + r * 128) | ((uint32_t)(r & 7) << 16) | ((uint32_t)(kc & 3) << 24);
+    }
+    load_group(cur, kb_begin);
+  }
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -177,7 +203,6 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
     }
     mbar_init(accum_bar, 1);
     s_abort = 0;
-    s_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -192,34 +217,6 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   const uint32_t smem_base = smem_u32(smem);
 
   if (warp < kProducerWarps) {
-    // ---- weight producers: 16 KiB of int8 per stage, 4 x 16 bytes per thread ----------------------
-    // chunk c = i*256 + tid covers row c/8, bytes (c%8)*16..+16 of the stage's 128 K elements.
-    const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.W);
-    const unsigned char* src[4];
-    uint32_t dst[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = i * 256 + tid, r = c >> 3, kc = c & 7;
-      const int row = min(row0 + r, p.N - 1);
-      src[i] = wbase + (size_t)row * p.ld + kc * 16;
-      // 16 int8 -> 32 bytes of fp16 = chunks 2*(kc&3), 2*(kc&3)+1 of atom kc>>2, XOR-swizzled by the row
-      dst[i] = (uint32_t)((kc >> 2) * (kBM * 128) + r * 128) | ((uint32_t)(r & 7) << 16) | ((uint32_t)(kc & 3) << 24);
-    }
-    // Loads are issued a GROUP of kGroup K blocks at a time (512 contiguous bytes of every row), one group
-    // ahead of the one being widened: 64 KiB in flight per CTA hides the HBM latency, and asking for 512 bytes
-    // of a row at once - instead of 128 bytes now and the next 128 a microsecond later - is what keeps the DRAM
-    // pages open (a 2 KiB weight row is one page; 148 CTAs x 128 rows thrash the banks otherwise).
-    constexpr int kGroup = 4;
-    int4 cur[kGroup][4], nxt[kGroup][4];
-    auto load_group = [&](int4 (&g)[kGroup][4], int kb0) {
-#pragma unroll
-      for (int d = 0; d < kGroup; ++d)
-        if (kb0 + d < kb_end) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) g[d][i] = (p.debug & 1) ? make_int4(kb0, d, i, 1) : ld_stream_16(src[i] + (size_t)(kb0 + d) * kBK);
-        }
-    };
-    load_group(cur, kb_begin);
     bool stop = false;
     for (int kb0 = kb_begin; kb0 < kb_end && !stop; kb0 += kGroup) {
       if (kb0 + kGroup < kb_end) load_group(nxt, kb0 + kGroup);
@@ -249,11 +246,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
           widen4((uint32_t)cur[d][i].z, h[4], h[5]);
           widen4((uint32_t)cur[d][i].w, h[6], h[7]);
           const uint32_t rowbase = a_stage + (dst[i] & 0xFFFF), sw = (dst[i] >> 16) & 7, c0 = ((dst[i] >> 24) & 3) * 2;
-          if (p.debug & 64) continue;
           asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + ((c0 ^ sw) << 4)), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
           asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rowbase + (((c0 + 1) ^ sw) << 4)), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
         }
-        if (!(p.debug & 32)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
         __syncwarp();
         if (lane == 0) mbar_arrive(full0 + 8 * s);
       }
@@ -277,7 +273,6 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
         }
         const uint32_t bar = full0 + 8 * s;
         const uint32_t b_stage = smem_base + s * kStageBytes + kATileBytes;
-        if (p.debug & 16) { mbar_arrive(bar); continue; }
         mbar_arrive_expect_tx(bar, 2 * kBTileBytes);
 #pragma unroll
         for (int plane = 0; plane < 2; ++plane) {
@@ -316,10 +311,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
             const uint64_t da = smem_desc(a_stage + atom * (kBM * 128) + ks * 32);
             const uint64_t dh = smem_desc(b_hi + atom * (BN * 128) + ks * 32);
             const uint64_t dl = smem_desc(b_lo + atom * (BN * 128) + ks * 32);
-            if (!(p.debug & 2)) {
-              umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
-              umma_f16(tmem, da, dl, idesc, 1u);
-            }
+            umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
+            umma_f16(tmem, da, dl, idesc, 1u);
           }
         }
         umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
@@ -347,8 +340,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
   const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
 
-  if (p.debug & 8) {
-  } else if (p.ksplit == 1) {
+  if (p.ksplit == 1) {
     if (epi_warp && have_acc) {
       const float ws = row < p.N ? p.scales[row] : 0.f;
 #pragma unroll 1
@@ -384,24 +376,28 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
         for (int j = 0; j < 16; ++j) my_part[(c0 + j) * kBM + quad * 32 + lane] = v[j];
       }
     }
+    // the row scales of this thread's four rows are fetched while the cluster barrier is pending
+    const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 8 columns in flight per pass
+    float wsc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wsc[i] = (row0 + r4 + i < p.N) ? __ldg(p.scales + row0 + r4 + i) : 0.f;
     cluster.sync();
     const int rank = (int)cluster.block_rank(), nranks = p.ksplit;
     // this CTA's columns: rank, rank + nranks, ...; 32 threads x float4 cover the 128 rows of a column
     if (tid < kProducerWarps * 32) {
-      const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 8 columns in flight per pass
       for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
+        const int m = m0 + c, rr = row0 + r4;
+        const float as = m < p.M ? __ldg(p.act_scale + m) : 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < nranks; ++r) {
           const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4);
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        const int m = m0 + c, rr = row0 + r4;
         if (m < p.M && rr < p.N) {
-          const float as = p.act_scale[m];
-          const float v0 = acc.x * p.scales[rr] * as;
-          const float v1 = rr + 1 < p.N ? acc.y * p.scales[rr + 1] * as : 0.f;
-          const float v2 = rr + 2 < p.N ? acc.z * p.scales[rr + 2] * as : 0.f;
-          const float v3 = rr + 3 < p.N ? acc.w * p.scales[rr + 3] * as : 0.f;
+          const float v0 = acc.x * wsc[0] * as;
+          const float v1 = acc.y * wsc[1] * as;
+          const float v2 = acc.z * wsc[2] * as;
+          const float v3 = acc.w * wsc[3] * as;
           if (p.epi == PI_EPI_SWIGLU) {
             float* o = p.out + (size_t)m * p.out_stride + (rr >> 1);
             if (rr + 1 < p.N) o[0] = silu_mul(v0, v1);
@@ -554,7 +550,7 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   const int M = a.M, K = (int)lin->cols, N = (int)lin->rows;
   const int BN = pick_bn(M);
   const int mtiles = (M + BN - 1) / BN, M_pad = mtiles * BN;
-  const int rtiles = (N + kBM - 1) / kBM, N_pad = rtiles * kBM;
+  const int rtiles = (N + kBM - 1) / kBM;
   const int nkb = K / kBK;
 
   // K splits: aim at ~1.5 CTAs per SM, at least two K blocks each.
@@ -565,23 +561,15 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
     while (ksplit * 2 <= want && ksplit < 8) ksplit *= 2;   // a portable cluster holds up to 8 CTAs
   }
 
-  // workspace: [act hi | act lo | act_scale] and [counters | partials]
+  // scratch (global memory beyond the inputs and outputs): [act hi | act lo | act_scale]
   const size_t plane = (size_t)M_pad * K * sizeof(__half);
   PI_TRY(pi_reserve(ctx, &ctx->gemm_act, 2 * plane + (size_t)M_pad * sizeof(float) + 256));
   __half* hi = static_cast<__half*>(ctx->gemm_act.ptr);
   __half* lo = hi + (size_t)M_pad * K;
   float* act_scale = reinterpret_cast<float*>(lo + (size_t)M_pad * K);
-  const size_t counters_bytes = 4096 * sizeof(int);
-  PI_REQUIRE(ctx, tiles <= 4096, "too many output tiles for the split-K counters");
-  const size_t part_bytes = ksplit > 1 ? (size_t)ksplit * M_pad * N_pad * sizeof(float) : 0;
-  if (ctx->gemm_partial.bytes < counters_bytes + part_bytes) {
-    PI_TRY(pi_reserve(ctx, &ctx->gemm_partial, counters_bytes + part_bytes));
-    PI_CUDA(ctx, cudaMemsetAsync(ctx->gemm_partial.ptr, 0, counters_bytes, ctx->stream));
-  }
 
   pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
-  const char* dbg_env = getenv("PI_GEMM_DEBUG");
-  if (!(dbg_env && (atoi(dbg_env) & 4))) {
+  {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(M);
     cfg.blockDim = dim3(256);
@@ -627,12 +615,7 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   p.ksplit = ksplit;
   p.nkb = nkb;
   p.epi = a.epi;
-  p.counters = static_cast<int*>(ctx->gemm_partial.ptr);
-  p.partial = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_partial.ptr) + counters_bytes);
-  p.part_row_stride = N_pad;
-  p.part_split_stride = (size_t)M_pad * N_pad;
   p.err_flag = ctx->dev_err;
-  { const char* dbg = getenv("PI_GEMM_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
   const dim3 grid(rtiles, ksplit, mtiles);
   cudaError_t e;
   switch (BN) {
