@@ -149,6 +149,26 @@ pi_status pi_linear_read_i8(pi_ctx* ctx, const pi_linear* lin, int8_t* q_host_ou
 pi_status pi_linear_apply(pi_ctx* ctx, const pi_linear* lin, const float* x_dev, float* out_dev, int M);
 /* Same with host buffers: copies x in, runs, copies out back, synchronises. */
 pi_status pi_linear_apply_host(pi_ctx* ctx, const pi_linear* lin, const float* x_host, float* out_host, int M);
+/* pi_linear_apply for callers that must not allocate while they run it.  This
+ * entry point has no counterpart in the reference.  The tensor-core projection
+ * keeps two fp16 planes of the activations and one factor per activation row
+ * in scratch memory; pi_linear_apply grows that scratch with cudaMalloc when a
+ * larger shape arrives.  A caller that is inside a CUDA stream capture, that has
+ * a latency budget a driver allocation would break, or that has given all
+ * device memory to its own pool cannot afford that, so this variant uses a
+ * fixed scratch area built into the library (about 2 MiB, held by every GPU
+ * that loads the library until the process exits) and calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *  - Limits: int8 projection with >= 32 rows and a multiple of 128 columns,
+ *    columns <= 8192, 1 <= M <= 64.  Anything else returns PI_ERR_INVALID_ARG.
+ *  - x_dev is [M x cols], out_dev is [M x rows], both dense, as in pi_linear_apply;
+ *    the work is ordered on the context's stream.
+ *  - The first call on a device looks up the scratch area's device address and
+ *    sets a kernel attribute; make that first call before any stream capture.
+ *  - The scratch area is shared by all calls on the device and keeps the last
+ *    call's contents; nothing in it needs clearing, but two calls whose kernels
+ *    overlap on the GPU (other streams or contexts) race on it: order them. */
+pi_status pi_linear_apply_noalloc(pi_ctx* ctx, const pi_linear* lin, const float* x_dev, float* out_dev, int M);
 
 /* ---- KV pool ------------------------------------------------------------------ */
 

@@ -90,6 +90,7 @@ SIGNATURES = {
     "pi_linear_read_i8": (_I, [_P, _P, _P, _P]),
     "pi_linear_apply": (_I, [_P, _P, _P, _P, _I]),
     "pi_linear_apply_host": (_I, [_P, _P, _P, _P, _I]),
+    "pi_linear_apply_noalloc": (_I, [_P, _P, _P, _P, _I]),
     "pi_kv_pool_create": (_I, [_P, C.POINTER(KvLayoutC), _PP]),
     "pi_kv_pool_destroy": (None, [_P]),
     "pi_kv_pool_bytes": (_SZ, [_P]),

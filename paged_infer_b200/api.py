@@ -252,6 +252,18 @@ class Projection:
         check(_lib.lib().pi_linear_apply(self.ctx.handle, self.handle, _dev_ptr(x_dev), _dev_ptr(out_dev), batch), self.ctx.handle)
 
 
+    def apply_device_noalloc(self, x_dev, out_dev, batch: int) -> None:
+        """``apply_device`` through the entry point that allocates nothing (``pi_linear_apply_noalloc``).
+
+        For callers that cannot let the library grow its scratch while they run a projection: code inside a
+        CUDA stream capture, latency-bound loops, embedders that own all device memory.  It works out of a
+        fixed scratch area that is part of the library, so it only takes int8 projections with a multiple of
+        128 columns (at most 8192) and 1..64 activation rows; anything larger raises ``PiError``.  Calls that
+        overlap on the GPU share that area and must be ordered by the caller.
+        """
+        check(_lib.lib().pi_linear_apply_noalloc(self.ctx.handle, self.handle, _dev_ptr(x_dev), _dev_ptr(out_dev), batch), self.ctx.handle)
+
+
 QuantizedLinear = Projection
 PackedLinear = Projection
 

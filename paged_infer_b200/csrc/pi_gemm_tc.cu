@@ -628,3 +628,131 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   ctx->launches++;
   return PI_OK;
 }
+
+// ---- pi_linear_apply_noalloc -----------------------------------------------------------------------------------
+//
+// The tensor-core projection needs scratch in global memory: the two fp16 planes (hi, lo) the f32 activations are
+// split into, plus one power-of-two factor per activation row.  pi_linear_apply takes that scratch from a buffer the
+// context grows with cudaMalloc on demand.  Some callers must not allocate at the moment they run a projection:
+// a serving loop that is inside a CUDA stream capture (cudaMalloc is not a capturable operation and invalidates
+// the capture), a host thread with a latency budget that a driver allocation (which can take the device-wide
+// allocation lock and synchronise) would break, or an embedder that has handed all device memory to its own pool.
+// For them the same kernels run here against a fixed scratch area that is part of the library image: every GPU
+// that loads the library carries kNoAllocScratchBytes (about 2 MiB) of it until the process exits.
+//
+// Limits: int8 projections the tensor path supports (columns a multiple of 128), 1 <= M <= 64 activation rows,
+// columns <= 8192.  Larger shapes are refused with PI_ERR_INVALID_ARG; they are never silently routed elsewhere.
+//
+// The area is shared by every call on the device and keeps whatever the previous call left in it.  Nothing in it
+// has to start at zero: rows [0, M) of both planes and the M factors are rewritten by every call before they are
+// read, and rows >= M are never read (the TMA descriptor is M rows tall, so a box that reaches past row M is
+// zero-filled by the copy engine rather than fetched).  Two calls whose kernels overlap on the GPU - different
+// streams, or different contexts on one device - would overwrite each other's planes: callers must order them.
+//
+// Set-up happens inside the first call on each device: the address of the area is looked up with
+// cudaGetSymbolAddress and, the first time each tile width is used, the kernel's shared-memory limit is raised
+// with cudaFuncSetAttribute.  Neither allocates, but make that first call before any stream capture begins.
+// The call itself never calls cudaMalloc, cudaFree, or any allocating library routine.
+constexpr int kNoAllocMaxM = 64;
+constexpr int kNoAllocMaxK = 8192;
+constexpr size_t kNoAllocScratchBytes =
+    2 * (size_t)kNoAllocMaxM * kNoAllocMaxK * sizeof(__half) + (size_t)kNoAllocMaxM * sizeof(float) + 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not an address a kernel could use.  Its device
+// address is looked up once per device, with that device current, and cached here.
+static void* g_noalloc_addr[64] = {};
+
+static pi_status noalloc_scratch_address(pi_ctx* ctx, void** out) {
+  PI_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "device index %d is outside the table of scratch addresses", ctx->device);
+  if (!g_noalloc_addr[ctx->device]) {
+    int current = -1;
+    PI_CUDA(ctx, cudaGetDevice(&current));
+    if (current != ctx->device) PI_CUDA(ctx, cudaSetDevice(ctx->device));
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (current != ctx->device) cudaSetDevice(current);
+    if (e != cudaSuccess || !ptr)
+      return pi_fail(ctx, PI_ERR_CUDA, "cudaGetSymbolAddress for the built-in scratch failed: %s", cudaGetErrorString(e));
+    g_noalloc_addr[ctx->device] = ptr;
+  }
+  *out = g_noalloc_addr[ctx->device];
+  return PI_OK;
+}
+
+extern "C" pi_status pi_linear_apply_noalloc(pi_ctx* ctx, const pi_linear* lin, const float* x_dev, float* out_dev, int M) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, lin && x_dev && out_dev, "null pointer");
+  PI_REQUIRE(ctx, M >= 1 && M <= kNoAllocMaxM, "batch %d is outside the built-in scratch (1..%d activation rows)", M, kNoAllocMaxM);
+  PI_REQUIRE(ctx, lin->cols <= (size_t)kNoAllocMaxK, "%zu columns exceed the built-in scratch (at most %d)", lin->cols, kNoAllocMaxK);
+  pi_linear_args a;
+  a.x = x_dev;
+  a.x_stride = lin->cols;
+  a.out = out_dev;
+  a.out_stride = lin->rows;
+  a.M = M;
+  PI_REQUIRE(ctx, pi_gemm_tc_supported(ctx, lin, a),
+             "the allocation-free projection needs an int8 matrix with at least 32 rows and a multiple of 128 columns");
+  void* scratch = nullptr;
+  PI_TRY(noalloc_scratch_address(ctx, &scratch));
+
+  const int K = (int)lin->cols, N = (int)lin->rows;
+  const int BN = pick_bn(M);
+  const int mtiles = 1, M_pad = BN;
+  const int rtiles = (N + kBM - 1) / kBM;
+  const int nkb = K / kBK;
+  int ksplit = 1;
+  if (rtiles < ctx->sm_count) {
+    const int want = std::min(std::max(1, (ctx->sm_count * 3 / 2) / rtiles), std::max(1, nkb / 2));
+    while (ksplit * 2 <= want && ksplit < 8) ksplit *= 2;
+  }
+  __half* hi = static_cast<__half*>(scratch);
+  __half* lo = hi + (size_t)M_pad * K;
+  float* act_scale = reinterpret_cast<float*>(lo + (size_t)M_pad * K);
+
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (size_t)K * sizeof(float);  // at most 32 KiB here: no attribute change needed
+    cfg.stream = ctx->stream;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, act_split_kernel, x_dev, (size_t)K, (const float*)nullptr, 0.f, K, hi, lo, act_scale);
+    if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
+    ctx->launches++;
+  }
+  CUtensorMap maps[2];
+  for (int i = 0; i < 2; ++i) {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+    const cuuint32_t box[2] = {64, (cuuint32_t)BN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode_tiled()(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, i == 0 ? (void*)hi : (void*)lo, dims, strides,
+                                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return pi_fail(ctx, PI_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  }
+  GemmParams p;
+  p.W = static_cast<const int8_t*>(lin->w);
+  p.scales = lin->scales;
+  p.act_scale = act_scale;
+  p.out = out_dev;
+  p.ld = lin->ld;
+  p.out_stride = lin->rows;
+  p.N = N;
+  p.K = K;
+  p.M = M;
+  p.ksplit = ksplit;
+  p.nkb = nkb;
+  p.epi = PI_EPI_STORE;
+  p.err_flag = ctx->dev_err;
+  const dim3 grid(rtiles, ksplit, mtiles);
+  cudaError_t e;
+  switch (BN) {
+    case 16: e = launch_tc<16, 4>(ctx, p, maps[0], maps[1], grid); break;
+    case 32: e = launch_tc<32, 4>(ctx, p, maps[0], maps[1], grid); break;
+    default: e = launch_tc<64, 3>(ctx, p, maps[0], maps[1], grid); break;
+  }
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
+  return PI_OK;
+}
