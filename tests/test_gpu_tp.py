@@ -1,0 +1,85 @@
+"""Tensor parallelism on two GPUs of one box (skipped where fewer are visible):
+each rank keeps its shard of the int8 weights and of the KV pool, the row-split
+projections are followed by one NCCL all-reduce, and the logits must agree with
+the single-GPU run of the same model within 1e-4 (only the summation order of the
+partial sums differs) and with the CPU oracle within 1e-3."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BLOCK = 16
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from oracle import pi_oracle as orc
+    from paged_infer_b200 import api
+    from paged_infer_b200.tp import exchange_unique_id
+    from test_gpu_model import kv_floats, small_llama
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ident = exchange_unique_id(api.nccl_unique_id, dist)
+        ctx = api.Context(rank, rank=rank, tp=world, nccl_id=ident)
+        cfg, om, gm = small_llama(ctx, orc, 9, kv_heads=2)          # 8 heads / 2 KV heads -> one KV head per rank
+        rng = np.random.default_rng(9)
+        B, nblocks = 6, 8
+        lens = [int(x) for x in rng.integers(5, 100, B)]
+        tables = [[b * nblocks + i for i in range(nblocks)] for b in range(B)]
+        kv = api.KvCache(ctx, gm.kv_layout(B * nblocks, BLOCK))
+        assert kv.layout.num_kv_heads == cfg.num_key_value_heads // world
+        prompts = [rng.integers(0, cfg.vocab_size, n).astype(np.uint32) for n in lens]
+        last = [gm.prefill_batched(p, 0, t, kv, 16) for p, t in zip(prompts, tables)]
+        tok = [int(np.argmax(l)) for l in last]
+        logits, ids = gm.decode_batch_into(tok, lens, tables, kv, want_argmax=True)
+        multi = gm.decode_multi(tok, lens, tables, kv, 5)             # overwrites position lens[b] with the same values
+        if rank == 0:
+            # the same model on one GPU, and on the CPU oracle
+            c1 = api.Context(0)
+            _, _, g1 = small_llama(c1, orc, 9, kv_heads=2)
+            kv1 = api.KvCache(c1, g1.kv_layout(B * nblocks, BLOCK))
+            okv = np.zeros(kv_floats(cfg, B * nblocks), np.float32)
+            for p, t in zip(prompts, tables):
+                g1.prefill_batched(p, 0, t, kv1, 16)
+                om.prefill_batched(p, 0, t, okv, BLOCK, 16)
+            l1, i1 = g1.decode_batch_into(tok, lens, tables, kv1, want_argmax=True)
+            m1 = g1.decode_multi(tok, lens, tables, kv1, 5)
+            lo = om.decode_batch(tok, lens, tables, okv, BLOCK)
+            out.put(("ok", float(np.abs(logits - l1).max()), float(np.abs(logits - lo).max()),
+                     ids.tolist() == i1.tolist(), multi.tolist() == m1.tolist()))
+        dist.barrier()
+    except Exception as e:  # noqa: BLE001
+        if rank == 0:
+            out.put(("fail", repr(e)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_matches_single_gpu_and_oracle():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 29700 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = out.get(timeout=600)
+    for p in procs:
+        p.join(120)
+    assert res[0] == "ok", res
+    _, d_single, d_oracle, same_ids, same_multi = res
+    assert d_single < 1e-4 and d_oracle < 1e-3 and same_ids and same_multi, res
