@@ -458,12 +458,103 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+LLAMA3_8B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                 intermediate_size=14336, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0)
+
+
+def run_tp_workload(args, rank: int, world: int, local_rank: int):
+    """`--workload llama3_8b_tp`: Llama-3-8B architecture, int8 projections, batch 32 decode at context 4096,
+    tensor-parallel over all `world` ranks (strong scaling: the total work is fixed)."""
+    import torch
+    import torch.distributed as dist
+
+    from paged_infer_b200 import api
+    from paged_infer_b200.loader import LlamaConfig
+    from paged_infer_b200.tp import exchange_unique_id
+
+    torch.cuda.set_device(local_rank)
+    ident = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        ident = exchange_unique_id(api.nccl_unique_id, dist)
+    hbm_peak, peak_kind = measured_peaks()
+    cfg = LlamaConfig(**LLAMA3_8B, quantization="int8")
+    B, CTX, K, W = 32, 4096, args.steps, max(args.warmup, 3)
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank, tp=world, nccl_id=ident)
+    model = api.LlamaWeights.synthetic(ctx, cfg, seed=3, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
+    blocks_per_seq = (CTX + K + W + BLOCK) // BLOCK + 1
+    kv = api.KvCache(ctx, model.kv_layout(B * blocks_per_seq, BLOCK))
+    kv.fill_normal(77 + rank, 1.0)
+    tables = [list(range(b * blocks_per_seq, (b + 1) * blocks_per_seq)) for b in range(B)]
+    rng = np.random.default_rng(3)
+    tokens = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)   # identical on every rank
+    pos = [CTX] * B
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out = model.decode_multi(tokens, pos, tables, kv, W)
+    tokens, pos = out[-1].copy(), [p + W for p in pos]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    ctx.reset_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    out = model.decode_multi(tokens, pos, tables, kv, K)
+    e1.record()
+    barrier()
+    t1 = time.time()
+    launches = ctx.kernel_launches()
+    clocks = sampler.stop(t0, t1)
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms[0])
+    # one profiled pass for the per-class shares (rank 0's view)
+    ctx.profile_begin()
+    model.decode_multi(out[-1].copy(), [p + K for p in pos], tables, kv, 2)
+    prof = ctx.profile_end()
+    if rank == 0:
+        total = sum(v[0] for v in prof.values()) or 1e-9
+        weight_bytes = model.weight_bytes()                         # this rank's shard
+        kv_bytes = B * (CTX + W + K // 2) * (cfg.num_key_value_heads // world) * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
+        step_ms = ms / K
+        line = {
+            "metric": "int8 batched paged decode throughput (Llama-3-8B arch, batch 32, context 4096, tensor parallel)",
+            "value": B * K / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 weights, f32 activations/accumulate/KV", "data": "synthetic",
+            "config": {"workload": "llama3_8b_tp", "batch": B, "context": CTX, "block_size": BLOCK, "parallelism": f"tp{world}",
+                       "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if world > 1 else 0,
+                       "weights": "N(0,0.02) generated on device, seed 3", "kv": "N(0,1) fill"},
+            "gpu_launches": launches, "clocks": clocks,
+            "step_roofline": {"bytes_per_step_per_gpu": weight_bytes + kv_bytes, "weight_bytes_per_gpu": weight_bytes,
+                              "kv_bytes_per_gpu": kv_bytes, "achieved_GB/s_per_gpu": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9, 1),
+                              "peak_GB/s": hbm_peak, "frac": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9 / hbm_peak, 3),
+                              "peak_kind": f"of {peak_kind}"},
+            "device_time_shares": {c: round(v[0] / total, 3) for c, v in prof.items() if v[0] > 0},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="tinyllama_b64_paged", choices=["tinyllama_b64_paged", "llama3_8b_tp"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -471,6 +562,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.workload == "llama3_8b_tp":
+        run_tp_workload(args, rank, world, local_rank)
         return
     run_gpu_arm(args, rank, world, local_rank)
 

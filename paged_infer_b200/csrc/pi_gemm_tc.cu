@@ -119,6 +119,14 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a, uint64_t b
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with the accumulate flag fixed to 1 (no predicate set-up per instruction).
+__device__ __forceinline__ void umma_f16_acc(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -303,16 +311,21 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_stage = smem_base + s * kStageBytes, b_hi = a_stage + kATileBytes, b_lo = b_hi + kBTileBytes;
+        // This one thread issues every MMA of the CTA, so its instruction count per K block bounds the whole
+        // pipeline: the three descriptors of a stage are built once and only their start-address field (low
+        // word, 16-byte units) is bumped by compile-time constants per MMA.
+        const uint32_t a_stage = smem_base + s * kStageBytes;
+        const uint64_t da0 = smem_desc(a_stage), dh0 = smem_desc(a_stage + kATileBytes), dl0 = smem_desc(a_stage + kATileBytes + kBTileBytes);
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {  // 16 K elements = 32 bytes per MMA
-            const uint64_t da = smem_desc(a_stage + atom * (kBM * 128) + ks * 32);
-            const uint64_t dh = smem_desc(b_hi + atom * (BN * 128) + ks * 32);
-            const uint64_t dl = smem_desc(b_lo + atom * (BN * 128) + ks * 32);
-            umma_f16(tmem, da, dh, idesc, (kb > kb_begin || atom > 0 || ks > 0) ? 1u : 0u);
-            umma_f16(tmem, da, dl, idesc, 1u);
+            const uint64_t da = da0 + (uint64_t)((atom * (kBM * 128) + ks * 32) >> 4);
+            const uint64_t dh = dh0 + (uint64_t)((atom * (BN * 128) + ks * 32) >> 4);
+            const uint64_t dl = dl0 + (uint64_t)((atom * (BN * 128) + ks * 32) >> 4);
+            if (atom == 0 && ks == 0) umma_f16(tmem, da, dh, idesc, kb > kb_begin ? 1u : 0u);
+            else umma_f16_acc(tmem, da, dh, idesc);
+            umma_f16_acc(tmem, da, dl, idesc);
           }
         }
         umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
@@ -426,6 +439,92 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
 }
 
 // ---- activation preparation: optional RMSNorm, power-of-two row scaling, fp16 hi/lo split ---------------------
+// Register-resident version: one CTA per activation row, the row is read from global memory exactly once
+// (VPT float4 per thread), two block reductions (sum of squares, then max |y|), one vectorised write per plane.
+template <int VPT>
+__global__ void __launch_bounds__(256) act_split_reg_kernel(const float* __restrict__ x, size_t x_stride,
+                                                            const float* __restrict__ norm_weight, float eps, int K,
+                                                            __half* __restrict__ hi, __half* __restrict__ lo,
+                                                            float* __restrict__ act_scale) {
+  __shared__ float red[8];
+  __shared__ float s_val;
+  pi_grid_dependency_wait();
+  const int m = blockIdx.x, tid = threadIdx.x, n4 = K >> 2;
+  const float4* row = reinterpret_cast<const float4*>(x + (size_t)m * x_stride);
+  float4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = tid + i * 256;
+    v[i] = idx < n4 ? row[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (norm_weight) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+    ss = pi_warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t += red[i];
+      s_val = 1.0f / sqrtf(t / (float)K + eps);
+    }
+    __syncthreads();
+    const float inv = s_val;
+    const float4* nw = reinterpret_cast<const float4*>(norm_weight);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = tid + i * 256;
+      if (idx < n4) {
+        const float4 w = __ldg(nw + idx);
+        v[i].x = v[i].x * inv * w.x;
+        v[i].y = v[i].y * inv * w.y;
+        v[i].z = v[i].z * inv * w.z;
+        v[i].w = v[i].w * inv * w.w;
+      }
+    }
+    __syncthreads();  // red[] and s_val are reused below
+  }
+  float mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+  mx = pi_warp_max(mx);
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t = fmaxf(t, red[i]);
+    int e = 0;
+    if (t > 0.f && t < INFINITY) frexpf(t, &e);
+    s_val = ldexpf(1.0f, -e);
+    act_scale[m] = ldexpf(1.0f, e);
+  }
+  __syncthreads();
+  const float s = s_val;
+  uint2* hrow = reinterpret_cast<uint2*>(hi + (size_t)m * K);
+  uint2* lrow = reinterpret_cast<uint2*>(lo + (size_t)m * K);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = tid + i * 256;
+    if (idx < n4) {
+      const float y[4] = {v[i].x * s, v[i].y * s, v[i].z * s, v[i].w * s};
+      __half h[4], l[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        h[j] = __float2half_rn(y[j]);
+        l[j] = __float2half_rn(y[j] - __half2float(h[j]));
+      }
+      hrow[idx] = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16),
+                             (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+      lrow[idx] = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
+                             (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+    }
+  }
+}
+
+// General version (any K): the normalised row is parked in shared memory between the passes.
 __global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict__ x, size_t x_stride,
                                                         const float* __restrict__ norm_weight, float eps, int K,
                                                         __half* __restrict__ hi, __half* __restrict__ lo,
@@ -585,7 +684,19 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
       PI_CUDA(ctx, cudaFuncSetAttribute(act_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes));
       split_granted = cfg.dynamicSmemBytes;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, act_split_kernel, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+    cudaError_t e;
+    const int n4 = K / 4;
+    const bool vec_ok = ((uintptr_t)a.x % 16 == 0) && (a.x_stride % 4 == 0) &&
+                        (!a.norm_weight || (uintptr_t)a.norm_weight % 16 == 0) && n4 <= 256 * 16;
+    if (vec_ok) {  // the row fits the registers of one CTA: single pass
+      cfg.dynamicSmemBytes = 0;
+      if (n4 <= 256 * 2) e = cudaLaunchKernelEx(&cfg, act_split_reg_kernel<2>, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+      else if (n4 <= 256 * 4) e = cudaLaunchKernelEx(&cfg, act_split_reg_kernel<4>, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+      else if (n4 <= 256 * 8) e = cudaLaunchKernelEx(&cfg, act_split_reg_kernel<8>, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+      else e = cudaLaunchKernelEx(&cfg, act_split_reg_kernel<16>, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+    } else {
+      e = cudaLaunchKernelEx(&cfg, act_split_kernel, a.x, a.x_stride, a.norm_weight, a.norm_eps, K, hi, lo, act_scale);
+    }
     if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
     ctx->launches++;
   }
