@@ -548,8 +548,74 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_kernel_case(args):
+    """`--kernel-case NAME`: a handful of launches of ONE kernel on a small case of the default workload's shapes,
+    for a profiler to capture (the numbers it prints itself are CUDA-event times of the same launches)."""
+    import torch
+
+    from paged_infer_b200 import api
+    from paged_infer_b200.loader import LlamaConfig
+
+    torch.cuda.set_device(0)
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    ctx = api.Context(0, stream=tstream.cuda_stream)
+    rng = np.random.default_rng(11)
+    reps = max(args.steps, 1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    case = args.kernel_case
+    if case in ("gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down"):
+        M = 1 if case.startswith("gemv") else 64
+        N, Kc = {"gemv_lm_head": (32000, 2048), "gemm_lm_head": (32000, 2048), "gemm_gate_up": (11264, 2048),
+                 "gemm_down": (2048, 5632)}[case]
+        q = rng.integers(-127, 128, (N, Kc), dtype=np.int8)
+        s = np.full(N, 1.6e-4, np.float32)
+        copies = 4                                            # rotate so that no launch finds its weights in L2
+        lins = [api.Projection.int8(ctx, q, s) for _ in range(copies)]
+        x = torch.randn(M, Kc, device="cuda", dtype=torch.float32)
+        y = torch.empty(M, N, device="cuda", dtype=torch.float32)
+        for l in lins:
+            l.apply_device(x, y, M)
+        torch.cuda.synchronize()
+        e0.record()
+        for r in range(reps):
+            lins[r % copies].apply_device(x, y, M)
+        e1.record()
+        torch.cuda.synchronize()
+        algo = N * Kc + 4 * N + 4 * M * Kc + 4 * M * N
+    elif case == "attention":
+        cfg = LlamaConfig(**TINYLLAMA, quantization="int8")
+        B, ctx_len = 64, 1024
+        nblk = ctx_len // BLOCK + 1
+        layout = api.KvLayout(1, B * nblk, BLOCK, cfg.num_key_value_heads, cfg.head_dim)
+        kv = api.KvCache(ctx, layout)
+        kv.fill_normal(9, 1.0)
+        attn = api.PagedAttention(layout, cfg.num_attention_heads)
+        qv = torch.randn(B, cfg.num_attention_heads * cfg.head_dim, device="cuda", dtype=torch.float32)
+        ov = torch.empty_like(qv)
+        entries = [api.AttnEntry(api.BlockTable(list(range(b * nblk, (b + 1) * nblk))), ctx_len - 1) for b in range(B)]
+        attn.run_device(qv, ov, kv, entries)
+        torch.cuda.synchronize()
+        e0.record()
+        for r in range(reps):
+            attn.run_device(qv, ov, kv, entries)
+        e1.record()
+        torch.cuda.synchronize()
+        algo = B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 + 2 * qv.numel() * 4
+    else:
+        raise SystemExit(f"unknown kernel case {case}")
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    hbm_peak, peak_kind = measured_peaks()
+    print(json.dumps({"kernel_case": case, "launch_groups": reps, "us_per_launch_group": round(us, 2),
+                      "algorithmic_bytes": int(algo), "GB/s": round(algo / us / 1e3, 1),
+                      "frac_of_hbm_peak": round(algo / us / 1e3 / hbm_peak, 3), "peak_kind": f"of {peak_kind}"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel-case", default=None,
+                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention"],
+                    help="run a few launches of one kernel on a small case (for a profiler) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
@@ -562,6 +628,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.kernel_case:
+        run_kernel_case(args)
         return
     if args.workload == "llama3_8b_tp":
         run_tp_workload(args, rank, world, local_rank)

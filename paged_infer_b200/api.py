@@ -401,6 +401,21 @@ class PagedAttention:
     def __init__(self, layout: KvLayout, num_heads: int, score_stride: int | None = None, heads_per_lane: int | None = None):
         self.layout, self.num_heads = layout, num_heads
 
+    def run_device(self, q_dev, out_dev, kv_cache: KvCache, entries, layer: int = 0) -> None:
+        """Same as ``run`` with q / out resident on the device (objects with ``data_ptr()``, dense f32
+        [entries][num_heads][head_dim]); asynchronous on the context's stream."""
+        B = len(entries)
+        if B == 0:
+            return
+        stride = self.num_heads * self.layout.head_dim
+        mat, lens, mb = pack_block_tables([e.block_table for e in entries])
+        pos = _i32([e.pos for e in entries])
+        start = _i32([e.start for e in entries])
+        check(_lib.lib().pi_paged_attention(kv_cache.ctx.handle, kv_cache.handle, layer, self.num_heads,
+                                            _dev_ptr(q_dev), stride, _dev_ptr(out_dev), stride,
+                                            _ptr(mat), mb if mb else 0, _ptr(lens), _ptr(pos), _ptr(start), B),
+              kv_cache.ctx.handle)
+
     def run(self, q, kv_cache: KvCache, entries, layer: int = 0) -> np.ndarray:
         """out [entries, num_heads, head_dim] for q of the same shape."""
         hd = self.layout.head_dim

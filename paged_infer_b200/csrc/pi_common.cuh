@@ -73,6 +73,7 @@ struct pi_ctx {
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
+  int opt_gemm_a_tmem = 1;  // tensor-core GEMM: 1 widened weights go to tensor memory (A operand from TMEM), 0 to shared memory
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
   bool prof_on = false;

@@ -438,6 +438,307 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   }
 }
 
+// ---- the same GEMM with the weight operand in tensor memory ----------------------------------------------------
+//
+// The kernel above is bound by shared-memory bandwidth, not by HBM: per K block every CTA writes 32 KiB of widened
+// weights to shared memory, the two MMAs of a K step each read the 4 KiB weight slice again, and the activation
+// planes add as much.  Here the widened weights never touch shared memory: a producer thread owns one weight row
+// (= one TMEM lane), loads 64 bytes of it straight from global memory with two 256-bit loads, widens them to 32
+// packed fp16 pairs and stores them with one tcgen05.st into the stage's 64 TMEM columns; the MMA takes A from TMEM.
+// The hi and lo activation planes are one B tile of 2*BN rows (hi rows, then lo rows), so one MMA per K step reads
+// the weights once and leaves W*hi in accumulator columns [0, BN) and W*lo in [BN, 2*BN); the epilogue adds them.
+// Shared memory then only carries the activation tiles (TMA in, MMA out).
+//
+// TMEM columns: [0, 2*BN) accumulator, then STAGES x 64 columns of widened weights.  The kernel always asks for
+// all 512 columns and for at least kMinSmem of shared memory, so two of these CTAs (or one of these and one of the
+// kernel above) never share an SM: a CTA blocked in tcgen05.alloc while its cluster peers wait for it at a cluster
+// barrier could otherwise deadlock.
+constexpr int kACols = kBK / 2;           // 128 fp16 of a row = 64 32-bit TMEM columns
+constexpr size_t kMinSmem = 120 * 1024;
+
+__device__ __forceinline__ void ld_stream_32(const void* p, uint32_t* v) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(p));
+}
+
+// 32 consecutive TMEM columns of this thread's lane (lane = 32 * (warp % 4) + laneid).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+
+// D[tmem_d] (+)= A[tmem_a] * B[smem descriptor]
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) {
+  constexpr int kBAtomBytes = 2 * BN * 128;                 // one 64-element K atom: BN hi rows, then BN lo rows
+  constexpr int kBStageBytes = 2 * kBAtomBytes;
+  constexpr int kDCols = 2 * BN;
+  static_assert(kDCols + STAGES * kACols <= 512, "TMEM holds 512 columns");
+  constexpr int kTmemCols = 512;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ uint32_t s_tmem;
+  __shared__ volatile int s_abort;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3, half = (warp >> 2) & 1;
+  const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
+  const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+
+  // ---- weight producers (warps 0-7): thread = weight row quad*32+lane, K half `half` of every K block ----------
+  // A GROUP of kGroup K blocks (2 x 32 bytes each) is requested one group ahead of the one being widened; the
+  // first group goes out before anything else in the kernel (weights never depend on the preceding kernel).
+  constexpr int kGroup = 4;
+  const unsigned char* src = nullptr;
+  uint32_t cur[kGroup][16], nxt[kGroup][16];
+  auto load_group = [&](uint32_t (&g)[kGroup][16], int kb0) {
+#pragma unroll
+    for (int d = 0; d < kGroup; ++d)
+      if (kb0 + d < kb_end) {
+        ld_stream_32(src + (size_t)(kb0 + d) * kBK, &g[d][0]);
+        ld_stream_32(src + (size_t)(kb0 + d) * kBK + 32, &g[d][8]);
+      }
+  };
+  if (warp < kProducerWarps) {
+    const int row = min(row0 + quad * 32 + lane, p.N - 1);
+    src = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * p.ld + half * 64;
+    load_group(cur, kb_begin);
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, kProducerWarps + 1);       // one arrival per producer warp + the TMA thread's expect_tx
+      mbar_init(empty0 + 8 * s, 1);                        // one tcgen05.commit
+    }
+    mbar_init(accum_bar, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == kProducerWarps + 1) {  // TMEM allocation is warp-wide
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  const uint32_t tmem_a0 = tmem + (uint32_t)kDCols;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp < kProducerWarps) {
+    bool stop = false;
+    const uint32_t my_a = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 32);
+    for (int kb0 = kb_begin; kb0 < kb_end && !stop; kb0 += kGroup) {
+      if (kb0 + kGroup < kb_end) load_group(nxt, kb0 + kGroup);
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d) {
+        const int kb = kb0 + d;
+        if (kb >= kb_end || stop) break;
+        const int it = kb - kb_begin, s = it % STAGES;
+        uint32_t h[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
+        // lane 0 polls for the whole warp
+        int ok = 1;
+        if (lane == 0) ok = (!s_abort && mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0 && !s_abort) {
+            s_abort = 1;
+            if (p.err_flag) atomicExch(p.err_flag, 2);
+          }
+          stop = true;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");   // the MMAs that read this stage are done
+        tmem_st32(my_a + (uint32_t)(s * kACols), h);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * s);
+      }
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) cur[d][i] = nxt[d][i];
+    }
+    pi_grid_dependency_wait();  // the epilogue below touches memory the producer kernel may still be writing
+  } else if (warp == kProducerWarps) {
+    // ---- activation loader: one 3-D TMA box {64 K, BN rows, 2 planes} per K atom -------------------------------
+    if (lane == 0) {
+      pi_grid_dependency_wait();  // the activation planes come from the preceding kernel
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin, s = it % STAGES;
+        if (s_abort) break;
+        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+          s_abort = 1;
+          if (p.err_flag) atomicExch(p.err_flag, 3);
+          break;
+        }
+        const uint32_t bar = full0 + 8 * s;
+        const uint32_t b_stage = smem_base + s * kBStageBytes;
+        mbar_arrive_expect_tx(bar, kBStageBytes);
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+                  b_stage + atom * kBAtomBytes),
+              "l"(&map_act), "r"(bar), "r"(kb * kBK + atom * 64), "r"(m0), "r"(0)
+              : "memory");
+        }
+      }
+    }
+  } else {
+    // ---- MMA issuer ------------------------------------------------------------------------------------------
+    if (lane == 0) {
+      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = f16, N = 2*BN, M = 128
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(kDCols >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        const int it = kb - kb_begin, s = it % STAGES;
+        if (s_abort || !mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) {
+          if (!s_abort && p.err_flag) atomicExch(p.err_flag, 4);
+          s_abort = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t db0 = smem_desc(smem_base + s * kBStageBytes);
+        const uint32_t a_s = tmem_a0 + (uint32_t)(s * kACols);
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {  // 16 K elements: 8 TMEM columns of A, 32 bytes of every B row
+            const uint64_t db = db0 + (uint64_t)((atom * kBAtomBytes + ks * 32) >> 4);
+            umma_f16_ts(tmem, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (kb > kb_begin || atom + ks > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty0 + 8 * s);  // the stage (TMEM columns and shared tile) is free once these MMAs are done
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  }
+
+  // ---- epilogue: warp w owns TMEM lanes 32*(w%4).., the two column halves go to warps 0-3 / 4-7 -----------------
+  bool have_acc = false;
+  if (warp < kProducerWarps) {
+    int got = 0;
+    if (lane == 0) {
+      got = ((kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0)) ? 1 : 0;
+      if (kb_begin < kb_end && !got && !s_abort) {
+        s_abort = 1;
+        if (p.err_flag) atomicExch(p.err_flag, 5);
+      }
+    }
+    have_acc = __shfl_sync(0xffffffffu, got, 0) != 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  const int row = row0 + quad * 32 + lane;
+  constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
+  const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
+  const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
+
+  if (p.ksplit == 1) {
+    if (epi_warp && have_acc) {
+      const float ws = row < p.N ? p.scales[row] : 0.f;
+#pragma unroll 1
+      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+        float v[16], w[16];
+        tmem_ld16(my_d + (uint32_t)c0, v);
+        tmem_ld16(my_d + (uint32_t)(BN + c0), w);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c0 + j;
+          const float as = m < p.M ? p.act_scale[m] : 0.f;
+          emit(p, m, row, (v[j] + w[j]) * ws * as, lane);
+        }
+      }
+    }
+  } else {
+    // K split over the CTAs of a cluster: same rank-ordered reduction through distributed shared memory as above.
+    cg::cluster_group cluster = cg::this_cluster();
+    float* my_part = reinterpret_cast<float*>(smem);  // [BN][128]
+    if (epi_warp) {
+#pragma unroll 1
+      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+        float v[16], w[16];
+        if (have_acc) {
+          tmem_ld16(my_d + (uint32_t)c0, v);
+          tmem_ld16(my_d + (uint32_t)(BN + c0), w);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = w[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) my_part[(c0 + j) * kBM + quad * 32 + lane] = v[j] + w[j];
+      }
+    }
+    const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 8 columns in flight per pass
+    float wsc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wsc[i] = (row0 + r4 + i < p.N) ? __ldg(p.scales + row0 + r4 + i) : 0.f;
+    cluster.sync();
+    const int rank = (int)cluster.block_rank(), nranks = p.ksplit;
+    if (tid < kProducerWarps * 32) {
+      for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
+        const int m = m0 + c, rr = row0 + r4;
+        const float as = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < nranks; ++r) {
+          const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (m < p.M && rr < p.N) {
+          const float v0 = acc.x * wsc[0] * as;
+          const float v1 = acc.y * wsc[1] * as;
+          const float v2 = acc.z * wsc[2] * as;
+          const float v3 = acc.w * wsc[3] * as;
+          if (p.epi == PI_EPI_SWIGLU) {
+            float* o = p.out + (size_t)m * p.out_stride + (rr >> 1);
+            if (rr + 1 < p.N) o[0] = silu_mul(v0, v1);
+            if (rr + 3 < p.N) o[1] = silu_mul(v2, v3);
+          } else {
+            float* o = p.out + (size_t)m * p.out_stride + rr;
+            const bool add = p.epi == PI_EPI_ADD;
+            o[0] = add ? o[0] + v0 : v0;
+            if (rr + 1 < p.N) o[1] = add ? o[1] + v1 : v1;
+            if (rr + 2 < p.N) o[2] = add ? o[2] + v2 : v2;
+            if (rr + 3 < p.N) o[3] = add ? o[3] + v3 : v3;
+          }
+        }
+      }
+    }
+    cluster.sync();  // nobody leaves while a peer may still be reading its tile
+  }
+  pi_grid_launch_dependents();
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kProducerWarps + 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
 // ---- activation preparation: optional RMSNorm, power-of-two row scaling, fp16 hi/lo split ---------------------
 // Register-resident version: one CTA per activation row, the row is read from global memory exactly once
 // (VPT float4 per thread), two block reductions (sum of squares, then max |y|), one vectorised write per plane.
@@ -632,6 +933,40 @@ cudaError_t launch_tc(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& hi, c
   return cudaLaunchKernelEx(&cfg, k, p, hi, lo);
 }
 
+template <int BN, int STAGES>
+cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, dim3 grid) {
+  constexpr size_t smem = std::max((size_t)STAGES * (4 * BN * 128) + 1024, kMinSmem);
+  auto k = gemm_ta_kernel<BN, STAGES>;
+  static bool granted = false;  // per instantiation
+  if (!granted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (ctx->opt_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (grid.y > 1) {  // the K slices of one row tile form a cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = grid.y;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, k, p, act);
+}
+
 }  // namespace
 
 bool pi_gemm_tc_supported(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
@@ -701,16 +1036,29 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
     ctx->launches++;
   }
 
+  const bool a_in_tmem = ctx->opt_gemm_a_tmem && ((uintptr_t)lin->w % 32 == 0) && (lin->ld % 32 == 0);
   CUtensorMap maps[2];
-  for (int i = 0; i < 2; ++i) {
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};          // innermost first; rows past M read as zero
-    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
-    const cuuint32_t box[2] = {64, (cuuint32_t)BN};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode_tiled()(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, i == 0 ? (void*)hi : (void*)lo, dims, strides, box,
-                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (a_in_tmem) {
+    // one map over both planes: {K, M rows (rows past M read as zero), 2 planes M_pad*K apart}
+    const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, 2};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * sizeof(__half), (cuuint64_t)M_pad * K * sizeof(__half)};
+    const cuuint32_t box[3] = {64, (cuuint32_t)BN, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_tiled()(&maps[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void*)hi, dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return pi_fail(ctx, PI_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  } else {
+    for (int i = 0; i < 2; ++i) {
+      const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};          // innermost first; rows past M read as zero
+      const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+      const cuuint32_t box[2] = {64, (cuuint32_t)BN};
+      const cuuint32_t estr[2] = {1, 1};
+      CUresult r = encode_tiled()(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, i == 0 ? (void*)hi : (void*)lo, dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return pi_fail(ctx, PI_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    }
   }
 
   GemmParams p;
@@ -729,11 +1077,20 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   p.err_flag = ctx->dev_err;
   const dim3 grid(rtiles, ksplit, mtiles);
   cudaError_t e;
-  switch (BN) {
-    case 16: e = launch_tc<16, 4>(ctx, p, maps[0], maps[1], grid); break;
-    case 32: e = launch_tc<32, 4>(ctx, p, maps[0], maps[1], grid); break;
-    case 64: e = launch_tc<64, 3>(ctx, p, maps[0], maps[1], grid); break;
-    default: e = launch_tc<128, 2>(ctx, p, maps[0], maps[1], grid); break;
+  if (a_in_tmem) {
+    switch (BN) {
+      case 16: e = launch_ta<16, 6>(ctx, p, maps[0], grid); break;
+      case 32: e = launch_ta<32, 6>(ctx, p, maps[0], grid); break;
+      case 64: e = launch_ta<64, 6>(ctx, p, maps[0], grid); break;
+      default: e = launch_ta<128, 3>(ctx, p, maps[0], grid); break;
+    }
+  } else {
+    switch (BN) {
+      case 16: e = launch_tc<16, 4>(ctx, p, maps[0], maps[1], grid); break;
+      case 32: e = launch_tc<32, 4>(ctx, p, maps[0], maps[1], grid); break;
+      case 64: e = launch_tc<64, 3>(ctx, p, maps[0], maps[1], grid); break;
+      default: e = launch_tc<128, 2>(ctx, p, maps[0], maps[1], grid); break;
+    }
   }
   if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
   ctx->launches++;

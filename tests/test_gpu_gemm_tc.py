@@ -51,6 +51,25 @@ def test_tensor_gemm_matches_cpu_matmat(ctx, oracle, rows, cols, M):
     assert rel_err(got / scale, slow / scale) < tol
 
 
+@pytest.mark.parametrize("rows,cols,M", [(2048, 2048, 64), (2560, 2048, 17), (2048, 5632, 130), (1000, 256, 5)])
+def test_both_weight_staging_variants_agree(ctx, oracle, rows, cols, M):
+    """The weight operand can be staged in tensor memory (default) or in shared memory; both must match the CPU."""
+    from paged_infer_b200 import api
+    q, s = oracle.quantize_rows_i8(normal_f32((rows, cols), rows + cols + 1, 0.02), rows, cols)
+    x = normal_f32((M, cols), M + 3, 1.0)
+    p = api.Projection.int8(ctx, q, s)
+    want = oracle.matmat_i8(x, q, s)
+    tol = 2e-5 * max(1.0, (cols / 2048.0) ** 0.5)
+    in_tmem = p.apply_batched(x)
+    ctx.set_option(api._lib.PI_OPT_GEMM_A_TMEM, 0)
+    try:
+        in_smem = p.apply_batched(x)
+    finally:
+        ctx.set_option(api._lib.PI_OPT_GEMM_A_TMEM, 1)
+    assert rel_err(in_tmem, want) < tol
+    assert rel_err(in_smem, want) < tol
+
+
 def test_tensor_gemm_really_ran(ctx, oracle):
     from paged_infer_b200 import api
     q, s = oracle.quantize_rows_i8(normal_f32((512, 512), 1, 0.02), 512, 512)
