@@ -42,6 +42,10 @@ sys.path.insert(0, ROOT)
 BLOCK = 16
 TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4,
                  intermediate_size=5632, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
+# DRAM traffic (dram__bytes_read + dram__bytes_write of one profiler capture) divided by the algorithmic bytes of the
+# same launch, per kernel class, from small single-kernel captures (`--kernel-case`, summaries under profiles/):
+# traffic of a bench launch = ratio x its algorithmic bytes (traffic grows in proportion to the rows / tokens streamed).
+NCU_TRAFFIC_RATIO = {"gemm_tc": 1.04, "gemv": 1.003, "attention": 1.03}
 GEMV_SHAPES = {"q/o 2048x2048": (2048, 2048), "k/v 256x2048": (256, 2048), "qkv fused 2560x2048": (2560, 2048),
                "gate/up 5632x2048": (5632, 2048), "down 2048x5632": (2048, 5632), "lm_head 32000x2048": (32000, 2048)}
 
@@ -385,9 +389,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         kv_bytes_layer = pb.unique_mapped_tokens() * KH * 2 * hd * 4
         algo = {"attention": kv_bytes_layer + 2 * B * H * hd * 4,
                 "gemv": weight_bytes / max(prof["gemv"][1] / P, 1), "gemm_tc": weight_bytes / max(prof["gemm_tc"][1] / P, 1)}
-        names = {"attention": "attn_decode_kernel<64,8> (+ split merge): one layer, 64 sequences",
+        names = {"attention": "attn_decode_v3_kernel<64,8,3> (+ split merge): one layer, 64 sequences",
                  "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step (average over the 5 matrices per layer)",
-                 "gemm_tc": "gemm_tc_kernel: tcgen05 dequant projections of the step (average over the 5 matrices per layer)"}
+                 "gemm_tc": "gemm_ta_kernel<64,6> (+ activation split): tcgen05 dequant projections of the step (average over its 89 launches)"}
         rl = {}
         for cls in ("attention", "gemv", "gemm_tc"):
             ms, n = prof[cls]
@@ -395,7 +399,9 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                 continue
             us = ms * 1e3 / n
             rl[cls] = {"kernel": names[cls], "bound": "hbm", "achieved": round(algo[cls] / us / 1e3, 1), "peak": hbm_peak,
-                       "unit": "GB/s", "frac": round(algo[cls] / us / 1e3 / hbm_peak, 3), "traffic": None,
+                       "unit": "GB/s", "frac": round(algo[cls] / us / 1e3 / hbm_peak, 3),
+                       "traffic": int(NCU_TRAFFIC_RATIO[cls] * algo[cls]),
+                       "traffic_source": f"ncu dram bytes of a single-kernel capture scaled by algorithmic bytes (x{NCU_TRAFFIC_RATIO[cls]})",
                        "us_per_launch": round(us, 2), "launches_per_step": n / P, "algorithmic_bytes_per_launch": int(algo[cls]),
                        "share_of_step_device_time": round(ms / total_ms, 3), "peak_kind": f"of {peak_kind}",
                        "timing": f"CUDA events around each of {n} launches inside {P} decode steps"}

@@ -172,6 +172,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_hi, c
   const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
   const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+  // Every thread releases the dependent grid right away (the release only happens once all threads of all CTAs
+  // have done so): the next kernels then sit resident, with their own prologue done, by the time this one ends.
+  pi_grid_launch_dependents();
 
   // ---- weight producers (warps 0-7): 16 KiB of int8 per stage, 4 x 16 bytes per thread ----------------------
   // chunk c = i*256 + tid covers row c/8, bytes (c%8)*16..+16 of the stage's 128 K elements.
@@ -502,6 +505,9 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
   const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+  // Every thread releases the dependent grid right away (the release only happens once all threads of all CTAs
+  // have done so): the next kernels then sit resident, with their own prologue done, by the time this one ends.
+  pi_grid_launch_dependents();
 
   // ---- weight producers (warps 0-7): thread = weight row quad*32+lane, K half `half` of every K block ----------
   // A GROUP of kGroup K blocks (2 x 32 bytes each) is requested one group ahead of the one being widened; the
@@ -702,10 +708,17 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
       for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
         const int m = m0 + c, rr = row0 + r4;
         const float as = m < p.M ? __ldg(p.act_scale + m) : 0.f;
+        // all peers' slices are requested before the first add (one remote latency instead of nranks), the adds
+        // stay in rank order
+        float4 part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[r] = r < nranks ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < nranks; ++r) {
-          const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
         }
         if (m < p.M && rr < p.N) {
           const float v0 = acc.x * wsc[0] * as;
@@ -987,11 +1000,12 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   const int rtiles = (N + kBM - 1) / kBM;
   const int nkb = K / kBK;
 
-  // K splits: aim at ~1.5 CTAs per SM, at least two K blocks each.
+  // K splits: as many as still fit in ONE wave (a CTA owns its SM, so a second, partly filled wave would cost a
+  // whole extra prologue + epilogue), at least two K blocks each.
   int ksplit = 1;
   const int tiles = rtiles * mtiles;
   if (tiles < ctx->sm_count) {
-    const int want = std::min(std::max(1, (ctx->sm_count * 3 / 2) / tiles), std::max(1, nkb / 2));
+    const int want = std::min(std::max(1, ctx->sm_count / tiles), std::max(1, nkb / 2));
     while (ksplit * 2 <= want && ksplit < 8) ksplit *= 2;   // a portable cluster holds up to 8 CTAs
   }
 
