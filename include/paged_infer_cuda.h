@@ -92,7 +92,7 @@ enum { PI_PROF_GEMV = 0, PI_PROF_GEMM_TC = 1, PI_PROF_ATTENTION = 2, PI_PROF_ROP
 pi_status pi_ctx_profile_begin(pi_ctx* ctx);
 pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out /*[PI_PROF_CLASSES]*/, uint64_t* launches_out /*[PI_PROF_CLASSES]*/);
 /* Tuning knobs (all default on): 0/1. */
-enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_GEMM_A_TMEM = 6 };
+enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6 };
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value);
 
 /* ---- quantiser --------------------------------------------------------------- */
@@ -156,7 +156,7 @@ pi_status pi_linear_apply_host(pi_ctx* ctx, const pi_linear* lin, const float* x
  * larger shape arrives.  A caller that is inside a CUDA stream capture, that has
  * a latency budget a driver allocation would break, or that has given all
  * device memory to its own pool cannot afford that, so this variant uses a
- * fixed scratch area built into the library (about 2 MiB, held by every GPU
+ * fixed scratch area built into the library (about 3 MiB, held by every GPU
  * that loads the library until the process exits) and calls no cudaMalloc,
  * cudaFree or other allocating routine.
  *  - Limits: int8 projection with >= 32 rows and a multiple of 128 columns,

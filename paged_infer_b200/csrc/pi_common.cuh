@@ -73,7 +73,7 @@ struct pi_ctx {
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
-  int opt_gemm_a_tmem = 1;  // tensor-core GEMM: 1 widened weights go to tensor memory (A operand from TMEM), 0 to shared memory
+  int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
   bool prof_on = false;
@@ -85,7 +85,7 @@ struct pi_ctx {
   pi_buffer staging_in, staging_out;   // device copies of host arguments / results
   pi_buffer attn_tables, attn_meta;    // block tables + per-entry (len, pos, start)
   pi_buffer attn_partial;              // split-KV partial (m, l, acc)
-  pi_buffer gemm_act;                  // fp16 hi/lo activation planes for the tensor GEMM
+  pi_buffer gemm_act;                  // bf16 activation planes (+ row factors) for the tensor GEMM
   pi_buffer gemm_partial;              // split-K partial sums
   void* pinned = nullptr;              // pinned host staging
   size_t pinned_bytes = 0;
@@ -120,6 +120,22 @@ enum pi_epilogue {
   PI_EPI_SWIGLU = 2     // rows interleaved gate/up: out[m][r/2] = silu(v[2i]) * v[2i+1]
 };
 
+// An activation matrix in the form the tensor-core GEMM consumes: three bf16 planes whose sum is the f32 value
+// exactly (plane 0 = bf16(y), plane 1 = bf16(y - p0), plane 2 = bf16(y - p0 - p1)), plus a per-row factor that the
+// consumer's epilogue multiplies back in.  For an RMS-normalised input y = x * norm_weight is what the planes hold and
+// the factor is 1/rms(x): either given directly (`row_scale`) or as per-tile partial sums of x^2 (`sumsq`), in which
+// case the factor is 1/sqrt(sum_over_tiles / K + eps).  Both null: factor 1.
+struct pi_act_planes {
+  __nv_bfloat16* base = nullptr;   // [3][rows_cap][K]
+  size_t plane_stride = 0;         // elements between planes
+  int K = 0;
+  float* row_scale = nullptr;      // [rows]
+  float* sumsq = nullptr;          // [sumsq_tiles][sumsq_stride]
+  int sumsq_tiles = 0;
+  size_t sumsq_stride = 0;
+  float eps = 0.f;
+};
+
 struct pi_linear_args {
   const float* x = nullptr;   // [M][x_stride]
   size_t x_stride = 0;
@@ -129,6 +145,14 @@ struct pi_linear_args {
   pi_epilogue epi = PI_EPI_STORE;
   const float* norm_weight = nullptr;  // fused RMSNorm prologue when non-null
   float norm_eps = 0.f;
+  // Tensor-core path only.  `in_planes`: x (after norm_weight, if any) is already available as planes, skip the
+  // split.  `emit`: besides `out`, write the result as planes for the next projection (base, plane_stride, K and the
+  // sumsq buffer are the caller's; with `emit_norm_weight` the planes hold out * weight and the kernel fills the
+  // per-tile sums of out^2 and sets sumsq_tiles).  Ask pi_gemm_tc_can_emit first.
+  const pi_act_planes* in_planes = nullptr;
+  pi_act_planes* emit = nullptr;
+  const float* emit_norm_weight = nullptr;
+  float emit_norm_eps = 0.f;
 };
 
 // CUDA-core dequant GEMV/GEMM (any shape, any M).
@@ -136,6 +160,13 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
 // tcgen05 tensor-core GEMM for int8 weights (returns PI_ERR_UNSUPPORTED when the shape does not fit).
 pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
 bool pi_gemm_tc_supported(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+// True when pi_linear_forward would take the tensor-core path for this call.
+bool pi_gemm_tc_will_run(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
+// True when that launch can also emit planes (and, with a norm weight, the partial sums of squares).
+bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, bool with_norm);
+// The activation split on its own (what the GEMM runs first when it is not given planes): x -> planes in `dst`.
+pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, const float* norm_weight, float eps, int M, int K,
+                              pi_act_planes* dst);
 // Dispatch between the two.
 pi_status pi_linear_forward(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
 

@@ -38,6 +38,11 @@ struct pi_model {
         *logits_gather = nullptr;
   uint32_t* tokens_dev = nullptr;
   uint32_t* argmax_dev = nullptr;
+  // activations handed from one tensor-core projection to the next as bf16 planes (tp == 1): the residual stream
+  // (times the next norm weight) and the SwiGLU output, plus the per-tile sums of squares of the residual rows
+  __nv_bfloat16 *planes_x = nullptr, *planes_h = nullptr;
+  float* sumsq = nullptr;
+  int sumsq_tiles_cap = 0;
   size_t weight_bytes = 0;
 };
 
@@ -286,6 +291,12 @@ pi_status build_model(pi_ctx* ctx, const pi_model_config* cfg, const ModelSource
   if (tp > 1) PI_TRY(alloc_f(ctx, &m->logits_gather, cap * vocab));
   PI_CUDA(ctx, cudaMalloc(&m->tokens_dev, cap * sizeof(uint32_t)));
   PI_CUDA(ctx, cudaMalloc(&m->argmax_dev, cap * sizeof(uint32_t)));
+  if (tp == 1) {
+    PI_CUDA(ctx, cudaMalloc(&m->planes_x, 3 * cap * hidden * sizeof(__nv_bfloat16)));
+    PI_CUDA(ctx, cudaMalloc(&m->planes_h, 3 * cap * (size_t)m->inter_local * sizeof(__nv_bfloat16)));
+    m->sumsq_tiles_cap = (hidden + 127) / 128;
+    PI_TRY(alloc_f(ctx, &m->sumsq, (size_t)m->sumsq_tiles_cap * cap));
+  }
   PI_TRY(ensure_rope(ctx, m, cfg->max_positions > 0 ? cfg->max_positions : 4096));
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return PI_OK;
@@ -302,14 +313,32 @@ __global__ void gather_logits_kernel(const float* __restrict__ in, float* __rest
   }
 }
 
-// run_layers_batch: leaves the residual stream (before the final norm) in m->x.
-pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_batch& batch, int B) {
+// What the last projection of run_layers left for the LM head when it could emit planes (tp == 1, tensor path).
+struct x_planes_state {
+  pi_act_planes planes;
+  bool valid = false;
+};
+
+// run_layers_batch: leaves the residual stream (before the final norm) in m->x.  On the tensor-core path with
+// tp == 1 the projections pass their result on as bf16 planes (already multiplied by the next norm weight, with the
+// sums of squares the next projection turns into 1/rms): o -> gate/up -> down -> next layer's q/k/v (or the LM
+// head, through `final_x`), so only the attention output and the embeddings go through the split kernel.
+pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_batch& batch, int B, x_planes_state* final_x) {
   const pi_model_config& c = m->cfg;
-  const int hidden = c.hidden_size, hd = m->hd;
+  const int hidden = c.hidden_size, hd = m->hd, L = c.num_hidden_layers;
   const size_t qrows = (size_t)m->heads_local * hd, kvrows = (size_t)m->kv_heads_local * hd;
   const size_t qkv_stride = qrows + 2 * kvrows;
+  const size_t cap = (size_t)m->capacity;
+  const bool fuse = ctx->opt_fuse_planes && ctx->tp == 1 && m->planes_x && m->planes_h;
+  pi_act_planes px, ph;                // residual-stream planes, SwiGLU-output planes
+  px.base = m->planes_x; px.plane_stride = cap * hidden; px.K = hidden;
+  px.sumsq = m->sumsq; px.sumsq_stride = cap;
+  ph.base = m->planes_h; ph.plane_stride = cap * (size_t)m->inter_local; ph.K = m->inter_local;
+  bool x_ready = false;                // px holds the planes of m->x for the next norm
+  if (final_x) final_x->valid = false;
+
   PI_TRY(pi_launch_embed(ctx, m->embed, c.vocab_size, hidden, m->tokens_dev, B, m->x));
-  for (int l = 0; l < c.num_hidden_layers; ++l) {
+  for (int l = 0; l < L; ++l) {
     pi_linear_args a;
     a.M = B;
     a.x = m->x;
@@ -318,10 +347,24 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     a.out_stride = qkv_stride;
     a.norm_weight = m->attn_norm[l];
     a.norm_eps = c.rms_norm_eps;
+    if (x_ready) a.in_planes = &px;
     PI_TRY(pi_linear_forward(ctx, m->qkv[l], a));
+    x_ready = false;
     PI_TRY(pi_launch_rope_kv_write(ctx, m->qkv_buf, qkv_stride, m->heads_local, m->kv_heads_local, hd, m->rope_cos,
                                    m->rope_sin, c.rope_style, pool, l, batch));
     PI_TRY(pi_launch_attention(ctx, pool, l, m->heads_local, m->qkv_buf, qkv_stride, m->attn_out, qrows, batch));
+
+    // gate/up consumes planes only if it runs on the tensor path itself
+    pi_linear_args g;
+    g.M = B;
+    g.x = m->x;
+    g.x_stride = hidden;
+    g.out = m->h;
+    g.out_stride = m->inter_local;
+    g.norm_weight = m->ffn_norm[l];
+    g.norm_eps = c.rms_norm_eps;
+    g.epi = PI_EPI_SWIGLU;
+    const bool g_tc = fuse && pi_gemm_tc_will_run(ctx, m->gate_up[l], g);
 
     pi_linear_args o;
     o.M = B;
@@ -337,24 +380,29 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
       o.out = m->x;
       o.out_stride = hidden;
       o.epi = PI_EPI_ADD;
+      if (g_tc && pi_gemm_tc_can_emit(ctx, m->wo[l], o, true)) {
+        o.emit = &px;
+        o.emit_norm_weight = m->ffn_norm[l];
+        o.emit_norm_eps = c.rms_norm_eps;
+        x_ready = true;
+      }
       PI_TRY(pi_linear_forward(ctx, m->wo[l], o));
     }
-
-    pi_linear_args g;
-    g.M = B;
-    g.x = m->x;
-    g.x_stride = hidden;
-    g.out = m->h;
-    g.out_stride = m->inter_local;
-    g.norm_weight = m->ffn_norm[l];
-    g.norm_eps = c.rms_norm_eps;
-    g.epi = PI_EPI_SWIGLU;
-    PI_TRY(pi_linear_forward(ctx, m->gate_up[l], g));
 
     pi_linear_args d;
     d.M = B;
     d.x = m->h;
     d.x_stride = m->inter_local;
+    const bool d_tc = fuse && pi_gemm_tc_will_run(ctx, m->down[l], d);
+    bool h_ready = false;
+    if (x_ready) g.in_planes = &px;
+    if (d_tc && pi_gemm_tc_can_emit(ctx, m->gate_up[l], g, false)) {
+      g.emit = &ph;
+      h_ready = true;
+    }
+    PI_TRY(pi_linear_forward(ctx, m->gate_up[l], g));
+    x_ready = false;
+
     if (ctx->tp > 1) {
       d.out = m->partial;
       d.out_stride = hidden;
@@ -365,14 +413,30 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
       d.out = m->x;
       d.out_stride = hidden;
       d.epi = PI_EPI_ADD;
+      if (h_ready) d.in_planes = &ph;
+      // the consumer of the new residual stream: the next layer's q/k/v, or the LM head over all B rows
+      const pi_linear* next = l + 1 < L ? m->qkv[l + 1] : (final_x ? m->lm_head : nullptr);
+      pi_linear_args nx;
+      nx.M = B;
+      if (fuse && next && pi_gemm_tc_will_run(ctx, next, nx) && pi_gemm_tc_can_emit(ctx, m->down[l], d, true)) {
+        d.emit = &px;
+        d.emit_norm_weight = l + 1 < L ? m->attn_norm[l + 1] : m->final_norm;
+        d.emit_norm_eps = c.rms_norm_eps;
+        x_ready = true;
+      }
       PI_TRY(pi_linear_forward(ctx, m->down[l], d));
     }
+  }
+  if (final_x && x_ready) {
+    final_x->planes = px;
+    final_x->valid = true;
   }
   return PI_OK;
 }
 
 // Final norm + LM head for `rows` rows of m->x starting at row `first`; logits land in m->logits [rows][vocab].
-pi_status project_logits(pi_ctx* ctx, pi_model* m, int first, int rows) {
+// `xp`: planes of all rows of m->x times the final norm weight, when run_layers left them (first must be 0).
+pi_status project_logits(pi_ctx* ctx, pi_model* m, int first, int rows, const x_planes_state* xp = nullptr) {
   const pi_model_config& c = m->cfg;
   pi_linear_args a;
   a.M = rows;
@@ -392,6 +456,7 @@ pi_status project_logits(pi_ctx* ctx, pi_model* m, int first, int rows) {
   } else {
     a.out = m->logits;
     a.out_stride = c.vocab_size;
+    if (xp && xp->valid && first == 0) a.in_planes = &xp->planes;
     PI_TRY(pi_linear_forward(ctx, m->lm_head, a));
   }
   return PI_OK;
@@ -524,7 +589,8 @@ void pi_model_destroy(pi_model* m) {
   for (float* p : m->ffn_norm) cudaFree(p);
   for (void* p : {(void*)m->embed, (void*)m->final_norm, (void*)m->rope_cos, (void*)m->rope_sin, (void*)m->x,
                   (void*)m->qkv_buf, (void*)m->attn_out, (void*)m->h, (void*)m->partial, (void*)m->logits,
-                  (void*)m->logits_gather, (void*)m->tokens_dev, (void*)m->argmax_dev})
+                  (void*)m->logits_gather, (void*)m->tokens_dev, (void*)m->argmax_dev, (void*)m->planes_x,
+                  (void*)m->planes_h, (void*)m->sumsq})
     if (p) cudaFree(p);
   delete m;
 }
@@ -543,8 +609,9 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
   PI_TRY(check_pool(ctx, m, pool));
   pi_attn_batch batch;
   PI_TRY(stage_batch(ctx, m, pool, tokens_host, positions_host, block_tables_host, max_blocks, table_lens_host, B, &batch));
-  PI_TRY(run_layers(ctx, m, pool, batch, B));
-  PI_TRY(project_logits(ctx, m, 0, B));
+  x_planes_state xs;
+  PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
+  PI_TRY(project_logits(ctx, m, 0, B, &xs));
   PI_TRY(fetch_results(ctx, m, B, logits_host_or_null, argmax_host_or_null));
   if (logits_host_or_null || argmax_host_or_null) return pi_ctx_synchronize(ctx);
   return PI_OK;
@@ -575,8 +642,9 @@ static __global__ void next_step_kernel(int* step_counter) {
 
 static pi_status decode_one_step(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_batch& batch, int B,
                                  uint32_t* history, int* step_counter) {
-  PI_TRY(run_layers(ctx, m, pool, batch, B));
-  PI_TRY(project_logits(ctx, m, 0, B));
+  x_planes_state xs;
+  PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
+  PI_TRY(project_logits(ctx, m, 0, B, &xs));
   PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
   advance_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(m->tokens_dev, m->argmax_dev, history, step_counter,
@@ -671,7 +739,7 @@ pi_status pi_model_prefill(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uin
     }
     pi_attn_batch batch;
     PI_TRY(stage_batch(ctx, m, pool, tokens_host + c0, pos.data(), tables.data(), table_len, lens.data(), len, &batch));
-    PI_TRY(run_layers(ctx, m, pool, batch, len));
+    PI_TRY(run_layers(ctx, m, pool, batch, len, nullptr));
     last_rows = len;
   }
   PI_TRY(project_logits(ctx, m, last_rows - 1, 1));

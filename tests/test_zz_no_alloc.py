@@ -5,7 +5,7 @@ allowed or not affordable - inside a CUDA stream capture (cudaMalloc cannot be
 captured), in a loop with a hard latency budget, or in a process that has handed
 all device memory to its own pool.  The library's normal projection call grows a
 scratch buffer with cudaMalloc when a bigger shape arrives; this variant works
-out of a fixed ~2 MiB area that is part of the library image instead.
+out of a fixed ~3 MiB area that is part of the library image instead.
 
 The test calls it through the C ABI twice in a row - the second call on a
 different matrix with fewer activation rows, so anything stale in the shared
