@@ -197,34 +197,6 @@ __device__ __forceinline__ void split3(float y, unsigned short& p0, unsigned sho
   p2 = __bfloat16_as_ushort(c);
 }
 
-// One value of the result as planes: element (m, col) of [3][.][emit_k].
-__device__ __forceinline__ void store_planes1(const GemmParams& p, int m, int col, float y) {
-  unsigned short a, b, c;
-  split3(y, a, b, c);
-  unsigned short* q = reinterpret_cast<unsigned short*>(p.emit_base) + (size_t)m * p.emit_k + col;
-  q[0] = a;
-  q[p.emit_plane_stride] = b;
-  q[2 * p.emit_plane_stride] = c;
-}
-
-// One output value through the epilogue (single-K-slice path).  SwiGLU pairs (gate, up) sit in adjacent rows =
-// adjacent lanes.  `nw` is the emit norm weight of this thread's output column (1 without).
-__device__ __forceinline__ void emit(const GemmParams& p, int m, int row, float v, int lane, float nw) {
-  if (p.epi == PI_EPI_SWIGLU) {
-    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-    if (!(lane & 1) && m < p.M && row + 1 < p.N) {
-      const float r = silu_mul(v, other);
-      p.out[(size_t)m * p.out_stride + (row >> 1)] = r;
-      if (p.emit_base) store_planes1(p, m, row >> 1, r * nw);
-    }
-  } else if (m < p.M && row < p.N) {
-    float* o = p.out + (size_t)m * p.out_stride + row;
-    const float r = (p.epi == PI_EPI_ADD) ? (*o + v) : v;
-    *o = r;
-    if (p.emit_base) store_planes1(p, m, row, r * nw);
-  }
-}
-
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) {
@@ -416,29 +388,18 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
     have_acc = __shfl_sync(0xffffffffu, got, 0) != 0;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
-  const int row = row0 + quad * 32 + lane;
   constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
   const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
   const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
 
-  if (p.ksplit == 1) {
-    if (epi_warp && have_acc) {
-      const float ws = row < p.N ? p.scales[row] : 0.f;
-      const int ecol = p.epi == PI_EPI_SWIGLU ? (row >> 1) : row;
-      const float nw = (p.emit_base && p.emit_norm && ecol < p.emit_k) ? __ldg(p.emit_norm + ecol) : 1.0f;
-#pragma unroll 1
-      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_ld_sum16<BN>(my_d, c0, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) emit(p, m0 + c0 + j, row, v[j] * ws * s_rowf[c0 + j], lane, nw);
-      }
-    }
-  } else {
-    // K was split over the CTAs of a thread-block cluster (cluster rank = K slice).  Every CTA parks its raw
-    // partial tile in its own shared memory (the pipeline stages are free by now), the cluster synchronises,
-    // and each CTA then adds up and emits 1/ksplit of the tile's columns, reading its peers' tiles through
-    // distributed shared memory in rank order - so the sum does not depend on timing.
+  {
+    // Every CTA parks its raw partial tile in its own shared memory (the pipeline stages are free by now).  When K
+    // was split over the CTAs of a thread-block cluster (cluster rank = K slice) the cluster synchronises and each
+    // CTA adds up and emits 1/ksplit of the tile's columns, reading its peers' tiles through distributed shared
+    // memory in rank order - so the sum does not depend on timing.  A single CTA goes the same way with itself as
+    // the only rank: the detour through shared memory turns the row-per-lane accumulator layout into four
+    // adjacent output columns per thread, so every store below is 8 or 16 bytes wide.
+    const bool clustered = p.ksplit > 1;
     cg::cluster_group cluster = cg::this_cluster();
     float* my_part = reinterpret_cast<float*>(smem);  // [BN][128]
     if (epi_warp) {
@@ -475,8 +436,8 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
         for (int i = 0; i < 4; ++i) nw[i] = __ldg(p.emit_norm + rr + i);
       }
     }
-    cluster.sync();
-    const int rank = (int)cluster.block_rank(), nranks = p.ksplit;
+    if (clustered) cluster.sync(); else __syncthreads();
+    const int rank = clustered ? (int)cluster.block_rank() : 0, nranks = p.ksplit;
     if (tid < kProducerWarps * 32) {
       for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
         const int m = m0 + c;
@@ -486,7 +447,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
         float4 part[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r)
-          part[r] = r < nranks ? *reinterpret_cast<const float4*>(cluster.map_shared_rank(my_part, r) + c * kBM + r4)
+          part[r] = r < nranks ? *reinterpret_cast<const float4*>((clustered ? cluster.map_shared_rank(my_part, r) : my_part) + c * kBM + r4)
                                : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -552,7 +513,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
         }
       }
     }
-    cluster.sync();  // nobody leaves while a peer may still be reading its tile
+    if (clustered) cluster.sync();  // nobody leaves while a peer may still be reading its tile
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -678,17 +639,6 @@ EncodeTiledFn encode_tiled() {
 
 int pick_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 
-// K splits: as many as still fit in ONE wave (a CTA owns its SM, so a second, partly filled wave would cost a
-// whole extra prologue + epilogue), at least two K blocks each.
-int pick_ksplit(const pi_ctx* ctx, int tiles, int nkb) {
-  int ksplit = 1;
-  if (tiles < ctx->sm_count) {
-    const int want = std::min(std::max(1, ctx->sm_count / tiles), std::max(1, nkb / 2));
-    while (ksplit * 2 <= want && ksplit < 8) ksplit *= 2;   // a portable cluster holds up to 8 CTAs
-  }
-  return ksplit;
-}
-
 template <int BN, int STAGES>
 cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, dim3 grid) {
   constexpr size_t smem = std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + 1024, kMinSmem);
@@ -723,6 +673,53 @@ cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, 
   return cudaLaunchKernelEx(&cfg, k, p, act);
 }
 
+// How many clusters of `ksplit` CTAs of this kernel the device can hold at once (clusters are placed inside one GPC,
+// so this is less than SMs / ksplit); asked once per cluster size.
+template <int BN, int STAGES>
+int max_clusters(pi_ctx* ctx, int ksplit) {
+  static int cached[9] = {};
+  if (ksplit < 2 || ksplit > 8) return ctx->sm_count;
+  if (!cached[ksplit]) {
+    constexpr size_t smem = std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + 1024, kMinSmem);
+    auto k = gemm_ta_kernel<BN, STAGES>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, ksplit, 1);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, k, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = std::max(1, ctx->sm_count / ksplit / 2);   // conservative
+    }
+    cached[ksplit] = n;
+  }
+  return cached[ksplit];
+}
+
+int max_clusters_bn(pi_ctx* ctx, int BN, int ksplit) {
+  switch (BN) {
+    case 16: return max_clusters<16, 6>(ctx, ksplit);
+    case 32: return max_clusters<32, 6>(ctx, ksplit);
+    default: return max_clusters<64, 4>(ctx, ksplit);
+  }
+}
+
+// K splits: as many as still run as ONE wave (a CTA owns its SM, so a second, partly filled wave would cost a
+// whole extra prologue + epilogue): the tiles' clusters must all be resident at once.  At least two K blocks each.
+int pick_ksplit(pi_ctx* ctx, int BN, int tiles, int nkb) {
+  for (int ksplit = 8; ksplit >= 2; ksplit >>= 1)
+    if (nkb / ksplit >= 2 && tiles * ksplit <= ctx->sm_count && tiles <= max_clusters_bn(ctx, BN, ksplit)) return ksplit;
+  return 1;
+}
+
 // The GEMM proper over activations that already are planes.
 pi_status run_gemm(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_act_planes& in) {
   const int M = a.M, K = (int)lin->cols, N = (int)lin->rows;
@@ -730,7 +727,7 @@ pi_status run_gemm(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, c
   const int mtiles = (M + BN - 1) / BN;
   const int rtiles = (N + kBM - 1) / kBM;
   const int nkb = K / kBK;
-  const int ksplit = pick_ksplit(ctx, rtiles * mtiles, nkb);
+  const int ksplit = pick_ksplit(ctx, BN, rtiles * mtiles, nkb);
   PI_REQUIRE(ctx, in.K == K && in.base, "activation planes do not match the projection (%d columns, planes of %d)", K, in.K);
 
   // one map over the three planes: {K, M rows (rows past M read as zero), 3 planes plane_stride apart}
@@ -828,13 +825,7 @@ bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linea
   if (!pi_gemm_tc_will_run(ctx, lin, a)) return false;
   const int N = (int)lin->rows;
   if (N % 4 != 0) return false;                           // planes are written four (two) columns at a time
-  if (with_norm) {
-    // the partial sums of squares are produced by the cluster epilogue only, and make no sense after SwiGLU here
-    if (a.epi == PI_EPI_SWIGLU) return false;
-    const int BN = pick_bn(a.M);
-    const int tiles = ((N + kBM - 1) / kBM) * ((a.M + BN - 1) / BN);
-    if (pick_ksplit(ctx, tiles, (int)lin->cols / kBK) == 1) return false;
-  }
+  if (with_norm && a.epi == PI_EPI_SWIGLU) return false;  // sums of squares of a SwiGLU output are not produced
   return true;
 }
 
