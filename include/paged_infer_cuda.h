@@ -151,7 +151,7 @@ pi_status pi_linear_apply(pi_ctx* ctx, const pi_linear* lin, const float* x_dev,
 pi_status pi_linear_apply_host(pi_ctx* ctx, const pi_linear* lin, const float* x_host, float* out_host, int M);
 /* pi_linear_apply for callers that must not allocate while they run it.  This
  * entry point has no counterpart in the reference.  The tensor-core projection
- * keeps two fp16 planes of the activations and one factor per activation row
+ * keeps three bf16 planes of the activations and one factor per activation row
  * in scratch memory; pi_linear_apply grows that scratch with cudaMalloc when a
  * larger shape arrives.  A caller that is inside a CUDA stream capture, that has
  * a latency budget a driver allocation would break, or that has given all

@@ -5,10 +5,10 @@
 //   out[m][r] = scale[r] * row_factor[m] * sum_k W[r][k] * y[m][k]
 //
 // Swap-AB: the 128 weight rows of a CTA sit on the MMA's M axis, the batch on its N
-// axis.  A producer thread owns one weight row (= one TMEM lane): it loads 64 bytes
-// of the row with two 256-bit loads, widens the int8 codes to bf16 (exact) in
-// registers and stores the 32 packed pairs with one tcgen05.st into the stage's 64
-// TMEM columns; the MMA takes A from TMEM, so widened weights never touch shared
+// axis.  A producer thread owns one weight row (= one TMEM lane): it loads 32 bytes
+// of the row with one 256-bit load, widens the int8 codes to bf16 (exact) in
+// registers and stores the 16 packed pairs with one tcgen05.st into the stage's 64
+// TMEM columns (four threads, in four warps, share a row's K block); the MMA takes A from TMEM, so widened weights never touch shared
 // memory.  Each f32 activation y is carried as three bf16 planes whose sum is y
 // exactly (p0 = bf16(y), p1 = bf16(y - p0), p2 = bf16(y - p0 - p1)); the three
 // planes of a K atom are ONE B tile of 3*BN rows fetched by one 3-D TMA box
@@ -23,9 +23,9 @@
 // f32 result and, in the same pass, the three planes of result * next_norm_weight
 // and per-tile partial sums of result^2, from which the consumer derives 1/rms.
 //
-// Warp roles (10 warps): 0-7 stream + widen the weights and later run the epilogue
-// out of TMEM; warp 8 issues the TMA loads of the activations; warp 9 allocates
-// TMEM and issues the MMAs.  Stages are handed over with mbarriers; every wait is
+// Warp roles (18 warps): 0-15 stream + widen the weights and later run the epilogue
+// (0-7 read the accumulator out of TMEM); warp 16 issues the TMA loads of the
+// activations; warp 17 allocates TMEM and issues the MMAs.  Stages are handed over with mbarriers; every wait is
 // bounded and a wait that runs out raises the context's error word instead of
 // hanging.
 //
@@ -51,7 +51,8 @@ namespace {
 
 constexpr int kBM = 128;            // weight rows per CTA (MMA M)
 constexpr int kBK = 128;            // K elements per pipeline stage (two 128-byte swizzle atoms of 16-bit elements)
-constexpr int kProducerWarps = 8;
+constexpr int kProducerWarps = 16;  // stream + widen the weights; all of them emit the result
+constexpr int kParkWarps = 8;       // warps 0-7 also move the accumulator from TMEM to shared memory
 constexpr int kThreads = (kProducerWarps + 2) * 32;
 constexpr uint32_t kSpinLimit = 1u << 21;
 constexpr int kPlanes = 3;
@@ -171,15 +172,12 @@ __device__ __forceinline__ void tmem_ld_sum16(uint32_t lane_base, int c, float* 
   for (int i = 0; i < 16; ++i) v[i] = (__uint_as_float(a[i]) + __uint_as_float(b[i])) + __uint_as_float(d[i]);
 }
 
-// 32 consecutive TMEM columns of this thread's lane (lane = 32 * (warp % 4) + laneid).
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+// 16 consecutive TMEM columns of this thread's lane (lane = 32 * (warp % 4) + laneid).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
-      "r"(r[31])
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 
@@ -215,7 +213,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   __shared__ float s_rowf[BN];     // row factor of the activation rows of this CTA
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int quad = warp & 3, half = (warp >> 2) & 1;
+  const int quad = warp & 3, kq = (warp >> 2) & 3, half = (warp >> 2) & 1;
   const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
   const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
@@ -223,23 +221,20 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   // have done so): the next kernels then sit resident, with their own prologue done, by the time this one ends.
   pi_grid_launch_dependents();
 
-  // ---- weight producers (warps 0-7): thread = weight row quad*32+lane, K half `half` of every K block ----------
-  // A GROUP of kGroup K blocks (2 x 32 bytes each) is requested one group ahead of the one being widened; the
-  // first group goes out before anything else in the kernel (weights never depend on the preceding kernel).
+  // ---- weight producers (warps 0-15): thread = weight row quad*32+lane, K quarter `kq` of every K block --------
+  // A GROUP of kGroup K blocks (32 bytes each) is requested one group ahead of the one being widened; the first
+  // group goes out before anything else in the kernel (weights never depend on the preceding kernel).
   constexpr int kGroup = 4;
   const unsigned char* src = nullptr;
-  uint32_t cur[kGroup][16], nxt[kGroup][16];
-  auto load_group = [&](uint32_t (&g)[kGroup][16], int kb0) {
+  uint32_t cur[kGroup][8], nxt[kGroup][8];
+  auto load_group = [&](uint32_t (&g)[kGroup][8], int kb0) {
 #pragma unroll
     for (int d = 0; d < kGroup; ++d)
-      if (kb0 + d < kb_end) {
-        ld_stream_32(src + (size_t)(kb0 + d) * kBK, &g[d][0]);
-        ld_stream_32(src + (size_t)(kb0 + d) * kBK + 32, &g[d][8]);
-      }
+      if (kb0 + d < kb_end) ld_stream_32(src + (size_t)(kb0 + d) * kBK, &g[d][0]);
   };
   if (warp < kProducerWarps) {
     const int row = min(row0 + quad * 32 + lane, p.N - 1);
-    src = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * p.ld + half * 64;
+    src = reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * p.ld + kq * 32;
     load_group(cur, kb_begin);
   }
 
@@ -266,7 +261,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
 
   if (warp < kProducerWarps) {
     bool stop = false;
-    const uint32_t my_a = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 32);
+    const uint32_t my_a = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(kq * 16);
     for (int kb0 = kb_begin; kb0 < kb_end && !stop; kb0 += kGroup) {
       if (kb0 + kGroup < kb_end) load_group(nxt, kb0 + kGroup);
 #pragma unroll
@@ -274,9 +269,9 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
         const int kb = kb0 + d;
         if (kb >= kb_end || stop) break;
         const int it = kb - kb_begin, s = it % STAGES;
-        uint32_t h[32];
+        uint32_t h[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
+        for (int i = 0; i < 8; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
         // lane 0 polls for the whole warp
         int ok = 1;
         if (lane == 0) ok = (!s_abort && mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) ? 1 : 0;
@@ -290,7 +285,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");   // the MMAs that read this stage are done
-        tmem_st32(my_a + (uint32_t)(s * kACols), h);
+        tmem_st16(my_a + (uint32_t)(s * kACols), h);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
@@ -299,7 +294,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
 #pragma unroll
       for (int d = 0; d < kGroup; ++d)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) cur[d][i] = nxt[d][i];
+        for (int i = 0; i < 8; ++i) cur[d][i] = nxt[d][i];
     }
     pi_grid_dependency_wait();  // the epilogue below touches memory the producer kernel may still be writing
     // row factors of this CTA's activation rows (1/rms from the partial sums of squares, in tile order)
@@ -376,7 +371,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
 
   // ---- epilogue: warp w owns TMEM lanes 32*(w%4).., the two column halves go to warps 0-3 / 4-7 -----------------
   bool have_acc = false;
-  if (warp < kProducerWarps) {
+  if (warp < kParkWarps) {
     int got = 0;
     if (lane == 0) {
       got = ((kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0)) ? 1 : 0;
@@ -389,7 +384,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
   constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
-  const bool epi_warp = warp < kProducerWarps && (BN >= 32 || half == 0);
+  const bool epi_warp = warp < kParkWarps && (BN >= 32 || half == 0);
   const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
 
   {
@@ -417,7 +412,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
       }
     }
     // this thread's four rows: scales and emit norm weights are fetched while the cluster barrier is pending
-    const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 8 columns in flight per pass
+    const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 16 columns in flight per pass
     const int rr = row0 + r4;
     float wsc[4], nw[4];
 #pragma unroll
@@ -715,7 +710,7 @@ int max_clusters_bn(pi_ctx* ctx, int BN, int ksplit) {
 // K splits: as many as still run as ONE wave (a CTA owns its SM, so a second, partly filled wave would cost a
 // whole extra prologue + epilogue): the tiles' clusters must all be resident at once.  At least two K blocks each.
 int pick_ksplit(pi_ctx* ctx, int BN, int tiles, int nkb) {
-  for (int ksplit = 8; ksplit >= 2; ksplit >>= 1)
+  for (int ksplit = 8; ksplit >= 2; --ksplit)   // a portable cluster holds up to 8 CTAs; any size below works
     if (nkb / ksplit >= 2 && tiles * ksplit <= ctx->sm_count && tiles <= max_clusters_bn(ctx, BN, ksplit)) return ksplit;
   return 1;
 }
