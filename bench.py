@@ -391,7 +391,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                 "gemv": weight_bytes / max(prof["gemv"][1] / P, 1), "gemm_tc": weight_bytes / max(prof["gemm_tc"][1] / P, 1)}
         names = {"attention": "attn_decode_v3_kernel<64,8,3> (+ split merge): one layer, 64 sequences",
                  "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step (average over the 5 matrices per layer)",
-                 "gemm_tc": "gemm_ta_kernel<64,6> (+ activation split): tcgen05 dequant projections of the step (average over its 89 launches)"}
+                 "gemm_tc": "gemm_ta_kernel<64,4> (+ the activation splits left): tcgen05 dequant projections of the step (average over its 89 launches)"}
         rl = {}
         for cls in ("attention", "gemv", "gemm_tc"):
             ms, n = prof[cls]
