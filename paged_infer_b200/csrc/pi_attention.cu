@@ -47,6 +47,9 @@ struct AttnParams {
   float* part_acc;  // [B][H][nsplit][HD]
   float scale;
   int* err_flag;
+  unsigned short* emit_base;   // merge kernel only: out as three bf16 planes [3][.][emit_k], or null
+  size_t emit_plane_stride;
+  int emit_k;
 };
 
 __device__ __forceinline__ float4 ldg_f4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
@@ -454,9 +457,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
   const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);
   const int nblk = (st <= pos && lb_begin + warp < lb_end) ? (lb_end - lb_begin - warp + kAttnWarps - 1) / kAttnWarps : 0;
 
-  auto issue = [&](int j) {
-    const int lb = lb_begin + warp + j * kAttnWarps;
-    const int pb = p.tables[(size_t)b * p.max_blocks + lb];
+  // physical block of this warp's tile j (lane 0 looks it up one tile ahead of the copy that needs it, so the
+  // table read is not on the path between two tiles)
+  auto lookup = [&](int j) { return p.tables[(size_t)b * p.max_blocks + lb_begin + warp + j * kAttnWarps]; };
+  auto issue = [&](int j, int pb) {
     const float* src = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kvh, 0);
     const uint32_t bar = attn_smem_u32(&bars[warp][j % STAGES]);
     const uint32_t dst = attn_smem_u32(ring + (size_t)(j % STAGES) * (kTileBytes / 4));
@@ -465,8 +469,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
                  "r"(kTileBytes), "r"(bar)
                  : "memory");
   };
-  if (lane == 0)
-    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j);
+  int pb_next = -1;
+  if (lane == 0) {
+    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j, lookup(j));
+    if (STAGES < nblk) pb_next = lookup(STAGES);
+  }
 
   // q: 8 dims per lane (16-byte chunks li and li + LPT of the head) for every head of the group, as float2 pairs
   float2 qv[G][4];
@@ -600,7 +607,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
       }
     }
     __syncwarp();
-    if (lane == 0 && j + STAGES < nblk) issue(j + STAGES);
+    if (lane == 0 && j + STAGES < nblk) {
+      issue(j + STAGES, pb_next);
+      if (j + 1 + STAGES < nblk) pb_next = lookup(j + 1 + STAGES);   // consumed one iteration from now
+    }
   }
 
   // ---- merge the token groups of the warp (the owned head's m, l; every head's accumulator) -------------------
@@ -685,7 +695,16 @@ __global__ void attn_combine_kernel(const AttnParams p, int HD) {
       ls += p.part_ml[(base + s) * 2 + 1] * f;
       a += p.part_acc[(base + s) * HD + d] * f;
     }
-    p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = a * (1.0f / fmaxf(ls, 1e-12f));
+    const float v = a * (1.0f / fmaxf(ls, 1e-12f));
+    p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = v;
+    if (p.emit_base) {
+      unsigned short p0, p1, p2;
+      pi_split3(v, p0, p1, p2);
+      unsigned short* q = p.emit_base + (size_t)b * p.emit_k + (size_t)h * HD + d;
+      q[0] = p0;
+      q[p.emit_plane_stride] = p1;
+      q[2 * p.emit_plane_stride] = p2;
+    }
   }
 }
 
@@ -868,7 +887,9 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
 }
 
 pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
-                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch) {
+                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch,
+                              pi_act_planes* emit, bool* emitted) {
+  if (emitted) *emitted = false;
   const pi_kv_layout& L = pool->L;
   PI_REQUIRE(ctx, layer >= 0 && layer < L.num_layers, "layer %d outside the pool's %d layers", layer, L.num_layers);
   PI_REQUIRE(ctx, L.num_kv_heads > 0 && num_heads % L.num_kv_heads == 0 && num_heads > 0,
@@ -894,6 +915,9 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   p.blocks_per_cta = std::max(batch.max_window_blocks, 1);
   p.part_ml = nullptr;
   p.part_acc = nullptr;
+  p.emit_base = nullptr;
+  p.emit_plane_stride = 0;
+  p.emit_k = 0;
 
   pi_prof_scope prof(ctx, PI_PROF_ATTENTION);
   const bool fast = (HD == 64 || HD == 128) && (group == 1 || group == 2 || group == 4 || group == 8) &&
@@ -940,6 +964,14 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
   ctx->launches++;
   if (nsplit > 1) {
+    if (emit && emit->base && emit->K == num_heads * HD) {
+      p.emit_base = reinterpret_cast<unsigned short*>(emit->base);
+      p.emit_plane_stride = emit->plane_stride;
+      p.emit_k = emit->K;
+      emit->row_scale = nullptr;
+      emit->sumsq_tiles = 0;
+      if (emitted) *emitted = true;
+    }
     e = launch_attn(ctx, attn_combine_kernel, dim3(num_heads, batch.B), dim3(HD), p, HD);
     if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "attention combine launch failed: %s", cudaGetErrorString(e));
     ctx->launches++;

@@ -205,8 +205,11 @@ struct pi_attn_batch {
 pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
                                const int32_t* pos_host, const int32_t* start_host, int B, int block_size,
                                pi_attn_batch* out);
+// `emit` (optional): when the KV axis is split and a merge kernel runs anyway, that kernel also writes the output as
+// bf16 planes (row factor 1) for the projection that follows; *emitted tells whether it did.
 pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
-                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
+                              size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch,
+                              pi_act_planes* emit = nullptr, bool* emitted = nullptr);
 
 // ---- glue ----------------------------------------------------------------------------
 pi_status pi_launch_embed(pi_ctx* ctx, const uint16_t* table_bf16, int vocab, int hidden, const uint32_t* tokens_dev,
@@ -241,6 +244,18 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
 
 // ---- device helpers ----------------------------------------------------------------------
 #ifdef __CUDACC__
+// y = p0 + p1 + p2 exactly, each a bf16 (each remainder has at most 16, then 8 significant bits left).
+__device__ __forceinline__ void pi_split3(float y, unsigned short& p0, unsigned short& p1, unsigned short& p2) {
+  const __nv_bfloat16 a = __float2bfloat16_rn(y);
+  const float r1 = y - __bfloat162float(a);
+  const __nv_bfloat16 b = __float2bfloat16_rn(r1);
+  const float r2 = r1 - __bfloat162float(b);
+  const __nv_bfloat16 c = __float2bfloat16_rn(r2);
+  p0 = __bfloat16_as_ushort(a);
+  p1 = __bfloat16_as_ushort(b);
+  p2 = __bfloat16_as_ushort(c);
+}
+
 __device__ __forceinline__ float pi_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

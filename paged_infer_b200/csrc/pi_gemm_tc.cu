@@ -183,17 +183,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
-// y = p0 + p1 + p2 exactly (each remainder has at most 16, then 8 significant bits left).
-__device__ __forceinline__ void split3(float y, unsigned short& p0, unsigned short& p1, unsigned short& p2) {
-  const __nv_bfloat16 a = __float2bfloat16_rn(y);
-  const float r1 = y - __bfloat162float(a);
-  const __nv_bfloat16 b = __float2bfloat16_rn(r1);
-  const float r2 = r1 - __bfloat162float(b);
-  const __nv_bfloat16 c = __float2bfloat16_rn(r2);
-  p0 = __bfloat16_as_ushort(a);
-  p1 = __bfloat16_as_ushort(b);
-  p2 = __bfloat16_as_ushort(c);
-}
+__device__ __forceinline__ void split3(float y, unsigned short& p0, unsigned short& p1, unsigned short& p2) { pi_split3(y, p0, p1, p2); }
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)

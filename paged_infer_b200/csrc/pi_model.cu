@@ -40,7 +40,7 @@ struct pi_model {
   uint32_t* argmax_dev = nullptr;
   // activations handed from one tensor-core projection to the next as bf16 planes (tp == 1): the residual stream
   // (times the next norm weight) and the SwiGLU output, plus the per-tile sums of squares of the residual rows
-  __nv_bfloat16 *planes_x = nullptr, *planes_h = nullptr;
+  __nv_bfloat16 *planes_x = nullptr, *planes_h = nullptr, *planes_a = nullptr;
   float* sumsq = nullptr;
   int sumsq_tiles_cap = 0;
   size_t weight_bytes = 0;
@@ -294,6 +294,7 @@ pi_status build_model(pi_ctx* ctx, const pi_model_config* cfg, const ModelSource
   if (tp == 1) {
     PI_CUDA(ctx, cudaMalloc(&m->planes_x, 3 * cap * hidden * sizeof(__nv_bfloat16)));
     PI_CUDA(ctx, cudaMalloc(&m->planes_h, 3 * cap * (size_t)m->inter_local * sizeof(__nv_bfloat16)));
+    PI_CUDA(ctx, cudaMalloc(&m->planes_a, 3 * cap * qrows * sizeof(__nv_bfloat16)));
     m->sumsq_tiles_cap = (hidden + 127) / 128;
     PI_TRY(alloc_f(ctx, &m->sumsq, (size_t)m->sumsq_tiles_cap * cap));
   }
@@ -330,10 +331,11 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
   const size_t qkv_stride = qrows + 2 * kvrows;
   const size_t cap = (size_t)m->capacity;
   const bool fuse = ctx->opt_fuse_planes && ctx->tp == 1 && m->planes_x && m->planes_h;
-  pi_act_planes px, ph;                // residual-stream planes, SwiGLU-output planes
+  pi_act_planes px, ph, pa;            // residual-stream planes, SwiGLU-output planes, attention-output planes
   px.base = m->planes_x; px.plane_stride = cap * hidden; px.K = hidden;
   px.sumsq = m->sumsq; px.sumsq_stride = cap;
   ph.base = m->planes_h; ph.plane_stride = cap * (size_t)m->inter_local; ph.K = m->inter_local;
+  pa.base = m->planes_a; pa.plane_stride = cap * qrows; pa.K = (int)qrows;
   bool x_ready = false;                // px holds the planes of m->x for the next norm
   if (final_x) final_x->valid = false;
 
@@ -352,7 +354,15 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     x_ready = false;
     PI_TRY(pi_launch_rope_kv_write(ctx, m->qkv_buf, qkv_stride, m->heads_local, m->kv_heads_local, hd, m->rope_cos,
                                    m->rope_sin, c.rope_style, pool, l, batch));
-    PI_TRY(pi_launch_attention(ctx, pool, l, m->heads_local, m->qkv_buf, qkv_stride, m->attn_out, qrows, batch));
+    pi_linear_args o;
+    o.M = B;
+    o.x = m->attn_out;
+    o.x_stride = qrows;
+    bool a_ready = false;              // the merge kernel of the attention wrote the output as planes too
+    const bool o_tc = fuse && m->planes_a && pi_gemm_tc_will_run(ctx, m->wo[l], o);
+    PI_TRY(pi_launch_attention(ctx, pool, l, m->heads_local, m->qkv_buf, qkv_stride, m->attn_out, qrows, batch,
+                               o_tc ? &pa : nullptr, &a_ready));
+    if (a_ready) o.in_planes = &pa;
 
     // gate/up consumes planes only if it runs on the tensor path itself
     pi_linear_args g;
@@ -366,10 +376,6 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     g.epi = PI_EPI_SWIGLU;
     const bool g_tc = fuse && pi_gemm_tc_will_run(ctx, m->gate_up[l], g);
 
-    pi_linear_args o;
-    o.M = B;
-    o.x = m->attn_out;
-    o.x_stride = qrows;
     if (ctx->tp > 1) {
       o.out = m->partial;
       o.out_stride = hidden;
@@ -590,7 +596,7 @@ void pi_model_destroy(pi_model* m) {
   for (void* p : {(void*)m->embed, (void*)m->final_norm, (void*)m->rope_cos, (void*)m->rope_sin, (void*)m->x,
                   (void*)m->qkv_buf, (void*)m->attn_out, (void*)m->h, (void*)m->partial, (void*)m->logits,
                   (void*)m->logits_gather, (void*)m->tokens_dev, (void*)m->argmax_dev, (void*)m->planes_x,
-                  (void*)m->planes_h, (void*)m->sumsq})
+                  (void*)m->planes_h, (void*)m->planes_a, (void*)m->sumsq})
     if (p) cudaFree(p);
   delete m;
 }
