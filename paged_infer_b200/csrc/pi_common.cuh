@@ -136,6 +136,21 @@ struct pi_act_planes {
   float eps = 0.f;
 };
 
+struct pi_kv_pool;
+struct pi_attn_batch;
+// Rotary embedding + KV write folded into the epilogue of the fused [q;k;v] projection (tensor-core path): the
+// kernel rotates the q and k heads (math::rope_rotate, src/math.rs:344-367), leaves q in `out` for the attention and
+// scatters k and v of every row into the pool at that row's position (write skipped when the logical block is not
+// mapped, src/model.rs:1094).  Ask pi_gemm_tc_can_rope first.
+struct pi_rope_kv {
+  int num_heads = 0, num_kv_heads = 0, head_dim = 0, style = 0;
+  const float* rope_cos = nullptr;   // [positions][head_dim/2]
+  const float* rope_sin = nullptr;
+  pi_kv_pool* pool = nullptr;
+  int layer = 0;
+  const pi_attn_batch* batch = nullptr;
+};
+
 struct pi_linear_args {
   const float* x = nullptr;   // [M][x_stride]
   size_t x_stride = 0;
@@ -153,6 +168,7 @@ struct pi_linear_args {
   pi_act_planes* emit = nullptr;
   const float* emit_norm_weight = nullptr;
   float emit_norm_eps = 0.f;
+  const pi_rope_kv* rope = nullptr;
 };
 
 // CUDA-core dequant GEMV/GEMM (any shape, any M).
@@ -164,6 +180,8 @@ bool pi_gemm_tc_supported(const pi_ctx* ctx, const pi_linear* lin, const pi_line
 bool pi_gemm_tc_will_run(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
 // True when that launch can also emit planes (and, with a norm weight, the partial sums of squares).
 bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, bool with_norm);
+// True when that launch can also apply the rotary embedding and write K/V into the pool.
+bool pi_gemm_tc_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r);
 // The activation split on its own (what the GEMM runs first when it is not given planes): x -> planes in `dst`.
 pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, const float* norm_weight, float eps, int M, int K,
                               pi_act_planes* dst);

@@ -83,6 +83,17 @@ struct GemmParams {
   const float* emit_norm;   // [emit_k] or null
   float* emit_sumsq;        // [row tiles][emit_sumsq_stride] or null
   size_t emit_sumsq_stride;
+  // optional: rotary embedding + KV write for the fused [q;k;v] projection (rope_hd = 0: off)
+  int rope_hd, rope_q_rows, rope_kv_rows, rope_style;
+  const float* rope_cos;
+  const float* rope_sin;
+  float* kv;
+  pi_kv_layout L;
+  int layer;
+  const int32_t* tables;
+  int max_blocks;
+  const int32_t* lens;
+  const int32_t* pos;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,6 +195,51 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
 __device__ __forceinline__ void split3(float y, unsigned short& p0, unsigned short& p1, unsigned short& p2) { pi_split3(y, p0, p1, p2); }
+
+// Epilogue of the fused [q;k;v] projection: thread = four adjacent output columns rr..rr+3 of activation row m,
+// all 32 lanes of the warp on the same m (so the shuffles below are safe).  Row tiles are whole heads: the NeoX
+// partner (j, j + hd/2) of a lane's four values sits in lane ^ (hd/8), interleaved pairs (2j, 2j+1) are the
+// thread's own.  q: rotated into out.  k: rotated into out and into the pool.  v: copied into the pool.
+__device__ __forceinline__ void emit_rope(const GemmParams& p, int m, int rr, int lane, float v0, float v1, float v2, float v3) {
+  const int hd = p.rope_hd, half = hd >> 1;
+  const bool valid = m < p.M && rr < p.N;
+  const int mm = valid ? m : 0;
+  const int seg = rr < p.rope_q_rows ? 0 : (rr < p.rope_q_rows + p.rope_kv_rows ? 1 : 2);   // q, k, v
+  const int within = rr - (seg == 0 ? 0 : (seg == 1 ? p.rope_q_rows : p.rope_q_rows + p.rope_kv_rows));
+  const int d = within % hd;             // first of this thread's four dims inside its head
+  const int position = p.pos[mm];
+  float r[4] = {v0, v1, v2, v3};
+  if (p.rope_style == 0) {
+    const int plane = hd >> 3;            // partner lane distance
+    const float o0 = __shfl_xor_sync(0xffffffffu, v0, plane), o1 = __shfl_xor_sync(0xffffffffu, v1, plane);
+    const float o2 = __shfl_xor_sync(0xffffffffu, v2, plane), o3 = __shfl_xor_sync(0xffffffffu, v3, plane);
+    if (seg < 2) {
+      const int j = d % half;
+      const float4 cs = __ldg(reinterpret_cast<const float4*>(p.rope_cos + (size_t)position * half + j));
+      const float4 sn = __ldg(reinterpret_cast<const float4*>(p.rope_sin + (size_t)position * half + j));
+      if (d < half) {    // this thread holds a = x[j..], the partner c = x[j + half..]:  a' = a*cos - c*sin
+        r[0] = v0 * cs.x - o0 * sn.x; r[1] = v1 * cs.y - o1 * sn.y; r[2] = v2 * cs.z - o2 * sn.z; r[3] = v3 * cs.w - o3 * sn.w;
+      } else {           // this thread holds c, the partner a:  c' = c*cos + a*sin
+        r[0] = v0 * cs.x + o0 * sn.x; r[1] = v1 * cs.y + o1 * sn.y; r[2] = v2 * cs.z + o2 * sn.z; r[3] = v3 * cs.w + o3 * sn.w;
+      }
+    }
+  } else if (seg < 2) {  // interleaved pairs (d, d+1), (d+2, d+3) with angles d/2, d/2 + 1
+    const int j = d >> 1;
+    const float c0 = __ldg(p.rope_cos + (size_t)position * half + j), s0 = __ldg(p.rope_sin + (size_t)position * half + j);
+    const float c1 = __ldg(p.rope_cos + (size_t)position * half + j + 1), s1 = __ldg(p.rope_sin + (size_t)position * half + j + 1);
+    r[0] = v0 * c0 - v1 * s0; r[1] = v1 * c0 + v0 * s0;
+    r[2] = v2 * c1 - v3 * s1; r[3] = v3 * c1 + v2 * s1;
+  }
+  if (!valid) return;
+  *reinterpret_cast<float4*>(p.out + (size_t)m * p.out_stride + rr) = make_float4(r[0], r[1], r[2], r[3]);
+  if (seg == 0) return;
+  const int lb = position / p.L.block_size, off = position % p.L.block_size;
+  if (lb >= p.lens[m]) return;             // unmapped: the write is skipped silently
+  const int pb = p.tables[(size_t)m * p.max_blocks + lb];
+  const int kh = within / hd;
+  float* dst = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kh, seg == 2 ? 1 : 0) + (size_t)off * hd + d;
+  *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -438,6 +494,10 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+        }
+        if (p.rope_hd) {   // fused [q;k;v] projection: rotary embedding + KV write (whole warp, same m)
+          emit_rope(p, m, rr, tid & 31, acc.x * wsc[0] * as, acc.y * wsc[1] * as, acc.z * wsc[2] * as, acc.w * wsc[3] * as);
+          continue;
         }
         float sq = 0.f;
         if (m < p.M && rr < p.N) {
@@ -767,6 +827,23 @@ pi_status run_gemm(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, c
       e->sumsq_tiles = 0;
     }
   }
+  if (a.rope) {
+    const pi_rope_kv& r = *a.rope;
+    PI_REQUIRE(ctx, pi_gemm_tc_can_rope(ctx, lin, a, r), "this launch cannot fold the rotary embedding and the KV write in");
+    p.rope_hd = r.head_dim;
+    p.rope_q_rows = r.num_heads * r.head_dim;
+    p.rope_kv_rows = r.num_kv_heads * r.head_dim;
+    p.rope_style = r.style;
+    p.rope_cos = r.rope_cos;
+    p.rope_sin = r.rope_sin;
+    p.kv = r.pool->data;
+    p.L = r.pool->L;
+    p.layer = r.layer;
+    p.tables = r.batch->tables;
+    p.max_blocks = r.batch->max_blocks;
+    p.lens = r.batch->lens;
+    p.pos = r.batch->pos;
+  }
   const dim3 grid(rtiles, ksplit, mtiles);
   cudaError_t err;
   switch (BN) {
@@ -812,6 +889,18 @@ bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linea
   if (N % 4 != 0) return false;                           // planes are written four (two) columns at a time
   if (with_norm && a.epi == PI_EPI_SWIGLU) return false;  // sums of squares of a SwiGLU output are not produced
   return true;
+}
+
+bool pi_gemm_tc_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r) {
+  if (!pi_gemm_tc_will_run(ctx, lin, a) || a.epi != PI_EPI_STORE || a.emit) return false;
+  if (!r.pool || !r.batch || !r.rope_cos || !r.rope_sin) return false;
+  if (r.head_dim != 64 && r.head_dim != 128) return false;            // a 128-row tile is whole heads
+  if (r.pool->L.head_dim != r.head_dim || r.pool->L.num_kv_heads != r.num_kv_heads) return false;
+  const size_t q_rows = (size_t)r.num_heads * r.head_dim, kv_rows = (size_t)r.num_kv_heads * r.head_dim;
+  if (q_rows % kBM != 0 || kv_rows % kBM != 0) return false;          // a tile is all q, all k or all v
+  if (lin->rows != q_rows + 2 * kv_rows) return false;
+  if ((uintptr_t)a.out % 16 != 0 || a.out_stride % 4 != 0) return false;
+  return r.style == 0 || r.style == 1;
 }
 
 pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, const float* norm_weight, float eps, int M, int K,

@@ -350,10 +350,23 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     a.norm_weight = m->attn_norm[l];
     a.norm_eps = c.rms_norm_eps;
     if (x_ready) a.in_planes = &px;
+    pi_rope_kv rk;
+    rk.num_heads = m->heads_local;
+    rk.num_kv_heads = m->kv_heads_local;
+    rk.head_dim = hd;
+    rk.style = c.rope_style;
+    rk.rope_cos = m->rope_cos;
+    rk.rope_sin = m->rope_sin;
+    rk.pool = pool;
+    rk.layer = l;
+    rk.batch = &batch;
+    const bool rope_fused = ctx->opt_fuse_planes && pi_gemm_tc_can_rope(ctx, m->qkv[l], a, rk);
+    if (rope_fused) a.rope = &rk;
     PI_TRY(pi_linear_forward(ctx, m->qkv[l], a));
     x_ready = false;
-    PI_TRY(pi_launch_rope_kv_write(ctx, m->qkv_buf, qkv_stride, m->heads_local, m->kv_heads_local, hd, m->rope_cos,
-                                   m->rope_sin, c.rope_style, pool, l, batch));
+    if (!rope_fused)
+      PI_TRY(pi_launch_rope_kv_write(ctx, m->qkv_buf, qkv_stride, m->heads_local, m->kv_heads_local, hd, m->rope_cos,
+                                     m->rope_sin, c.rope_style, pool, l, batch));
     pi_linear_args o;
     o.M = B;
     o.x = m->attn_out;

@@ -60,11 +60,12 @@ def test_llama3_and_llama2_70b_projection_shapes(ctx, oracle, rows, cols, M):
     assert rel_err(p.apply_batched(x), oracle.matmat_i8(x, q, s)) < 2e-5 * (cols / 2048.0) ** 0.5
 
 
-def wide_llama(ctx, oracle, seed, hidden, heads, kv_heads, inter, vocab, theta, layers=1, max_batch=64):
+def wide_llama(ctx, oracle, seed, hidden, heads, kv_heads, inter, vocab, theta, layers=1, max_batch=64, rope_style=0):
     """A full-width model with random RMSNorm weights (N(1, 0.2)) and an int8 LM head."""
     from paged_infer_b200 import api
     from paged_infer_b200.loader import HostWeights, LlamaConfig, f32_to_bf16_bits
     cfg = LlamaConfig(hidden, layers, heads, kv_heads, inter, vocab, 1e-5, theta, quantization="int8")
+    cfg.rope_style = rope_style
     hd = hidden // heads
     shapes = {"wq": (hidden, hidden), "wk": (kv_heads * hd, hidden), "wv": (kv_heads * hd, hidden),
               "wo": (hidden, hidden), "w1": (inter, hidden), "w2": (hidden, inter), "w3": (inter, hidden)}
@@ -144,6 +145,27 @@ def test_llama3_8b_width_one_layer(ctx, oracle):
                              max_batch=32)
     worst, mism = run_model_case(ctx, oracle, cfg, om, gm, prompt_len=40, batch=32)
     assert worst < 1e-3 and mism == 0, (worst, mism)
+
+
+@pytest.mark.parametrize("heads,kv_heads,style", [(16, 4, 1), (8, 2, 0), (8, 2, 1)])
+def test_rope_and_kv_write_in_the_projection_epilogue(ctx, oracle, heads, kv_heads, style):
+    """Batched decode folds the rotary embedding and the KV write into the q/k/v projection: both pairing styles,
+    head_dim 64 and 128, logits and the pool contents against the oracle."""
+    from paged_infer_b200 import api
+    cfg, om, gm = wide_llama(ctx, oracle, 31 + style, hidden=1024, heads=heads, kv_heads=kv_heads, inter=2816, vocab=2048,
+                             theta=10000.0, layers=2, rope_style=style)
+    rng = np.random.default_rng(5)
+    B, nblocks = 40, 48
+    okv = (rng.standard_normal(kv_floats(cfg, nblocks)) * 0.5).astype(np.float32)
+    gkv = api.KvCache(ctx, gm.kv_layout(nblocks, BLOCK))
+    gkv.upload(okv)
+    tables = [[b] for b in range(B)]
+    toks = [int(t) for t in rng.integers(0, cfg.vocab_size, B)]
+    pos = [int(p) for p in rng.integers(0, BLOCK, B)]
+    want = om.decode_batch(toks, pos, tables, okv, BLOCK)
+    got = gm.decode_batch_into(toks, pos, tables, gkv, want_logits=True)
+    assert np.abs(got - want).max() < 1e-3
+    assert np.abs(gkv.download() - okv).max() < 1e-4
 
 
 def test_two_layers_hand_planes_across_the_layer_boundary(ctx, oracle):
