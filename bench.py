@@ -476,7 +476,7 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
 
     from paged_infer_b200 import api
     from paged_infer_b200.loader import LlamaConfig
-    from paged_infer_b200.tp import exchange_unique_id
+    from paged_infer_b200.tp import enable_peer_exchange, exchange_unique_id
 
     torch.cuda.set_device(local_rank)
     ident = None
@@ -489,6 +489,12 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank, tp=world, nccl_id=ident)
+    exchange = "single GPU"
+    if world > 1:
+        exchange = "nccl all-reduce"
+        if not args.nccl_exchange:
+            enable_peer_exchange(ctx, B * cfg.hidden_size, dist)
+            exchange = "peer memory (P2P loads + flags, residual add folded in)"
     model = api.LlamaWeights.synthetic(ctx, cfg, seed=3, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
     blocks_per_seq = (CTX + K + W + BLOCK) // BLOCK + 1
     kv = api.KvCache(ctx, model.kv_layout(B * blocks_per_seq, BLOCK))
@@ -539,7 +545,7 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 weights, f32 activations/accumulate/KV", "data": "synthetic",
             "config": {"workload": "llama3_8b_tp", "batch": B, "context": CTX, "block_size": BLOCK, "parallelism": f"tp{world}",
-                       "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if world > 1 else 0,
+                       "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if world > 1 else 0, "exchange": exchange,
                        "weights": "N(0,0.02) generated on device, seed 3", "kv": "N(0,1) fill"},
             "gpu_launches": launches, "clocks": clocks,
             "step_roofline": {"bytes_per_step_per_gpu": weight_bytes + kv_bytes, "weight_bytes_per_gpu": weight_bytes,
@@ -628,6 +634,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="tinyllama_b64_paged", choices=["tinyllama_b64_paged", "llama3_8b_tp"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--nccl-exchange", action="store_true", help="llama3_8b_tp: all-reduce through NCCL instead of the peer-memory kernel")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: NCCL's own banner ("NCCL version ...") goes to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")

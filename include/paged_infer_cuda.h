@@ -76,6 +76,16 @@ pi_status pi_ctx_create(int device, void* stream, pi_ctx** out);
 pi_status pi_nccl_unique_id(void* out_128_bytes);
 pi_status pi_ctx_create_tp(int device, void* stream, int rank, int tp,
                            const void* nccl_unique_id, pi_ctx** out);
+/* Optional peer-memory path for the exchange after the row-split projections (o, down): instead of an NCCL
+ * all-reduce, one kernel per exchange reads every peer's partial sums straight out of that peer's memory (NVLink
+ * P2P loads), adds them in rank order and folds in the residual add.  Set-up: every rank calls
+ * pi_tp_peer_export(ctx, max_rows * hidden_size, handle) -> 64 bytes, the host gathers the tp handles in rank order
+ * (any transport) and every rank calls pi_tp_peer_import(ctx, all_handles).  Without it the NCCL path is used.
+ * Ranks must be processes on the GPUs of one node with peer access.  Waits on a peer are bounded: a rank whose
+ * peer never arrives reports PI_ERR_TIMEOUT at the next synchronising call.  No counterpart in the reference. */
+#define PI_TP_PEER_HANDLE_BYTES 64
+pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* handle_out_64_bytes);
+pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles_tp_times_64_bytes);
 void pi_ctx_destroy(pi_ctx* ctx);
 /* Block until everything queued on the context's stream has finished. */
 pi_status pi_ctx_synchronize(pi_ctx* ctx);

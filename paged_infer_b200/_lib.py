@@ -69,6 +69,8 @@ SIGNATURES = {
     "pi_ctx_create": (_I, [_I, _P, _PP]),
     "pi_nccl_unique_id": (_I, [_P]),
     "pi_ctx_create_tp": (_I, [_I, _P, _I, _I, _P, _PP]),
+    "pi_tp_peer_export": (_I, [_P, _SZ, _P]),
+    "pi_tp_peer_import": (_I, [_P, _P]),
     "pi_ctx_destroy": (None, [_P]),
     "pi_ctx_synchronize": (_I, [_P]),
     "pi_ctx_kernel_launches": (C.c_uint64, [_P]),

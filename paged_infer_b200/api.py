@@ -87,6 +87,19 @@ class Context:
     def set_option(self, option: int, value: int):
         check(_lib.lib().pi_ctx_set_option(self.handle, option, value), self.handle)
 
+    def tp_peer_export(self, max_floats: int) -> bytes:
+        """Allocate this rank's peer-readable exchange buffers (``max_floats`` = max rows x hidden) -> 64-byte handle."""
+        buf = C.create_string_buffer(64)
+        check(_lib.lib().pi_tp_peer_export(self.handle, max_floats, buf), self.handle)
+        return buf.raw
+
+    def tp_peer_import(self, handles) -> None:
+        """``handles``: the 64-byte handles of all ranks, in rank order."""
+        raw = b"".join(handles)
+        if len(raw) != 64 * self.tp:
+            raise PiError(_lib.PI_ERR_INVALID_ARG, "one 64-byte handle per rank is needed")
+        check(_lib.lib().pi_tp_peer_import(self.handle, C.create_string_buffer(raw, len(raw))), self.handle)
+
 
 def nccl_unique_id() -> bytes:
     buf = C.create_string_buffer(128)

@@ -66,6 +66,17 @@ struct pi_ctx {
   // tensor parallelism
   int rank = 0, tp = 1;
   void* nccl_comm = nullptr;  // ncclComm_t
+  // Peer-memory exchange for the row-split projections (optional, set up with pi_tp_peer_export/import): every rank
+  // owns `slots` buffers of partial sums that its peers read directly over NVLink, plus arrival flags they write.
+  struct {
+    bool ready = false;
+    size_t slot_floats = 0;
+    void* base = nullptr;                       // one allocation: [2 slots of floats | flags[2][8] | epoch[2] | ticket[2]]
+    float* data[8] = {};                        // slot 0 of every rank's buffer (own rank: local pointer)
+    unsigned long long* flags[8] = {};          // every rank's flag array
+    void* mapped[8] = {};                       // what cudaIpcOpenMemHandle returned (to close)
+    int next_slot = 0;
+  } peer;
 
   // options
   bool opt_tensor_gemm = true;
@@ -259,6 +270,11 @@ pi_status pi_tp_init(pi_ctx* ctx, const void* unique_id);
 void pi_tp_destroy(pi_ctx* ctx);
 pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n);
 pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t bytes_per_rank);
+// Peer path: where this rank's next row-split projection must write its [n] partial sums, and the kernel that waits
+// for all ranks' partials of that slot, adds them in rank order and adds the sum to x.
+bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n);
+float* pi_tp_peer_slot(pi_ctx* ctx);
+pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, size_t n);
 
 // ---- device helpers ----------------------------------------------------------------------
 #ifdef __CUDACC__

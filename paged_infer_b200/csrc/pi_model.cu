@@ -389,12 +389,17 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     g.epi = PI_EPI_SWIGLU;
     const bool g_tc = fuse && pi_gemm_tc_will_run(ctx, m->gate_up[l], g);
 
+    const bool peer = pi_tp_peer_usable(ctx, (size_t)B * hidden);   // partial sums exchanged through peer memory
     if (ctx->tp > 1) {
-      o.out = m->partial;
+      o.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       o.out_stride = hidden;
       PI_TRY(pi_linear_forward(ctx, m->wo[l], o));
-      PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
-      PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
+      if (peer) {
+        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, (size_t)B * hidden));
+      } else {
+        PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
+        PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
+      }
     } else {
       o.out = m->x;
       o.out_stride = hidden;
@@ -423,11 +428,15 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     x_ready = false;
 
     if (ctx->tp > 1) {
-      d.out = m->partial;
+      d.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       d.out_stride = hidden;
       PI_TRY(pi_linear_forward(ctx, m->down[l], d));
-      PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
-      PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
+      if (peer) {
+        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, (size_t)B * hidden));
+      } else {
+        PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
+        PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
+      }
     } else {
       d.out = m->x;
       d.out_stride = hidden;

@@ -4,6 +4,8 @@
 // all-gather.  NCCL is bound at run time (dlopen) so that single-GPU users do
 // not need it.  The reference has no multi-device code; nothing is replaced.
 #include <dlfcn.h>
+
+#include <algorithm>
 #include <nccl.h>
 
 #include "pi_common.cuh"
@@ -76,6 +78,16 @@ pi_status pi_tp_init(pi_ctx* ctx, const void* unique_id) {
 }
 
 void pi_tp_destroy(pi_ctx* ctx) {
+  for (int r = 0; r < 8; ++r)
+    if (ctx->peer.mapped[r]) {
+      cudaIpcCloseMemHandle(ctx->peer.mapped[r]);
+      ctx->peer.mapped[r] = nullptr;
+    }
+  if (ctx->peer.base) {
+    cudaFree(ctx->peer.base);
+    ctx->peer.base = nullptr;
+  }
+  ctx->peer.ready = false;
   if (ctx->nccl_comm) {
     nccl()->CommDestroy(static_cast<ncclComm_t>(ctx->nccl_comm));
     ctx->nccl_comm = nullptr;
@@ -95,5 +107,178 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
     return PI_OK;
   }
   PI_NCCL(ctx, nccl()->AllGather(send, recv, bytes_per_rank, ncclInt8, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->stream));
+  return PI_OK;
+}
+
+// ---- peer-memory exchange ----------------------------------------------------------------------------------------
+//
+// Layout of every rank's allocation: [slot 0 floats | slot 1 floats | flags[2][8] u64 | epoch[2] u64 | ticket[2] u32].
+// Two slots alternate between consecutive exchanges (o, down, o, ...).  A rank may overwrite slot s again only after
+// the exchange on slot 1-s, and that exchange cannot finish before every peer has started it, i.e. has finished
+// reading slot s: no reader is ever overtaken.
+namespace {
+constexpr int kPeerSlots = 2;
+constexpr int kPeerMaxTp = 8;
+constexpr uint32_t kPeerSpinLimit = 1u << 22;
+
+struct PeerReduceParams {
+  float* x;
+  size_t n4;                         // float4 count
+  int tp, rank, slot;
+  const float* data[kPeerMaxTp];     // this slot of every rank
+  unsigned long long* flags[kPeerMaxTp];   // flag arrays of every rank
+  unsigned long long* epoch;         // local: epoch[slot]
+  unsigned int* ticket;              // local: ticket[slot]
+  int* err_flag;
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {   // never from a stale L1 line
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// grid <= number of SMs (all CTAs resident: they all read the epoch before the last one to finish advances it).
+__global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduceParams p) {
+  __shared__ int s_ok;
+  pi_grid_dependency_wait();          // the partial sums of this rank come from the preceding kernel
+  const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(p.epoch) + 1ull;
+  if (blockIdx.x == 0 && threadIdx.x < p.tp && (int)threadIdx.x != p.rank) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + (size_t)p.slot * kPeerMaxTp + p.rank, e);   // "my slot is ready" on that peer
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < p.tp && ok; ++r) {
+      if (r == p.rank) continue;
+      const unsigned long long* f = p.flags[p.rank] + (size_t)p.slot * kPeerMaxTp + r;
+      uint32_t spin = 0;
+      while (ld_acquire_sys(f) < e) {
+        if (++spin >= kPeerSpinLimit) {
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    if (!ok && p.err_flag) atomicExch(p.err_flag, 9);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok) {
+    float4* x4 = reinterpret_cast<float4*>(p.x);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n4; i += (size_t)gridDim.x * blockDim.x) {
+      float4 part[kPeerMaxTp];
+#pragma unroll
+      for (int r = 0; r < kPeerMaxTp; ++r)
+        if (r < p.tp) part[r] = (r == p.rank) ? *reinterpret_cast<const float4*>(p.data[r] + 4 * i) : ld_peer_f4(p.data[r] + 4 * i);
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < kPeerMaxTp; ++r)   // rank order on every rank: all ranks get the same bits
+        if (r < p.tp) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
+      float4 v = x4[i];
+      v.x += sum.x; v.y += sum.y; v.z += sum.z; v.w += sum.w;
+      x4[i] = v;
+    }
+  }
+  // the last CTA to finish advances the epoch of this slot for the next exchange on it
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int t = atomicAdd(p.ticket, 1u);
+    if (t == gridDim.x - 1) {
+      *p.ticket = 0u;
+      *reinterpret_cast<volatile unsigned long long*>(p.epoch) = e;
+    }
+  }
+}
+
+size_t peer_flags_offset(size_t slot_floats) { return kPeerSlots * slot_floats * sizeof(float); }
+}  // namespace
+
+extern "C" pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* handle_out) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, handle_out && max_floats > 0, "null pointer or empty buffer");
+  PI_REQUIRE(ctx, ctx->tp > 1 && ctx->tp <= kPeerMaxTp, "the peer path needs a tensor-parallel context");
+  PI_REQUIRE(ctx, !ctx->peer.base, "the peer buffers of this context exist already");
+  static_assert(sizeof(cudaIpcMemHandle_t) == PI_TP_PEER_HANDLE_BYTES, "cudaIpcMemHandle_t is 64 bytes");
+  const size_t slot_floats = (max_floats + 63) / 64 * 64;
+  const size_t bytes = peer_flags_offset(slot_floats) + (kPeerSlots * kPeerMaxTp + kPeerSlots) * sizeof(unsigned long long) +
+                       kPeerSlots * sizeof(unsigned int) + 64;
+  PI_CUDA(ctx, cudaMalloc(&ctx->peer.base, bytes));
+  PI_CUDA(ctx, cudaMemset(ctx->peer.base, 0, bytes));
+  ctx->peer.slot_floats = slot_floats;
+  cudaIpcMemHandle_t h;
+  PI_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->peer.base));
+  memcpy(handle_out, &h, sizeof(h));
+  return PI_OK;
+}
+
+extern "C" pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, handles && ctx->peer.base, "call pi_tp_peer_export first");
+  const unsigned char* all = static_cast<const unsigned char*>(handles);
+  for (int r = 0; r < ctx->tp; ++r) {
+    void* base = ctx->peer.base;
+    if (r != ctx->rank) {
+      cudaIpcMemHandle_t h;
+      memcpy(&h, all + (size_t)r * sizeof(h), sizeof(h));
+      PI_CUDA(ctx, cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+      ctx->peer.mapped[r] = base;
+    }
+    ctx->peer.data[r] = static_cast<float*>(base);
+    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(base) + peer_flags_offset(ctx->peer.slot_floats));
+  }
+  ctx->peer.next_slot = 0;
+  ctx->peer.ready = true;
+  return PI_OK;
+}
+
+bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n) {
+  return ctx->tp > 1 && ctx->peer.ready && n <= ctx->peer.slot_floats && n % 4 == 0;
+}
+
+float* pi_tp_peer_slot(pi_ctx* ctx) { return ctx->peer.data[ctx->rank] + (size_t)ctx->peer.next_slot * ctx->peer.slot_floats; }
+
+pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, size_t n) {
+  PI_REQUIRE(ctx, pi_tp_peer_usable(ctx, n) && (uintptr_t)x % 16 == 0, "the peer exchange is not set up for %zu values", n);
+  pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
+  const int slot = ctx->peer.next_slot;
+  ctx->peer.next_slot ^= 1;
+  PeerReduceParams p = {};
+  p.x = x;
+  p.n4 = n / 4;
+  p.tp = ctx->tp;
+  p.rank = ctx->rank;
+  p.slot = slot;
+  for (int r = 0; r < ctx->tp; ++r) {
+    p.data[r] = ctx->peer.data[r] + (size_t)slot * ctx->peer.slot_floats;
+    p.flags[r] = ctx->peer.flags[r];
+  }
+  unsigned long long* epoch = ctx->peer.flags[ctx->rank] + kPeerSlots * kPeerMaxTp;
+  p.epoch = epoch + slot;
+  p.ticket = reinterpret_cast<unsigned int*>(epoch + kPeerSlots) + slot;
+  p.err_flag = ctx->dev_err;
+  const unsigned grid = (unsigned)std::min<size_t>((p.n4 + 255) / 256, (size_t)ctx->sm_count);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(std::max(grid, 1u));
+  cfg.blockDim = dim3(256);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, tp_peer_reduce_add_kernel, p);
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "peer exchange launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
   return PI_OK;
 }

@@ -56,3 +56,17 @@ def exchange_unique_id(make_id, dist) -> bytes:
         buf = buf.cuda()
     dist.broadcast(buf, src=0)
     return bytes(buf.cpu().tolist())
+
+
+def enable_peer_exchange(ctx, max_floats: int, dist) -> None:
+    """Set up the peer-memory path for the exchange after the row-split projections: every rank exports a handle
+    to its buffers (``max_floats`` = max batch rows x hidden size), the handles are all-gathered over ``dist``
+    (``torch.distributed``, any backend) and imported.  Without this call the NCCL all-reduce is used."""
+    import torch
+
+    mine = torch.tensor(list(ctx.tp_peer_export(max_floats)), dtype=torch.uint8)
+    if dist.get_backend() == "nccl":
+        mine = mine.cuda()
+    everyone = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(everyone, mine)
+    ctx.tp_peer_import([bytes(t.cpu().tolist()) for t in everyone])

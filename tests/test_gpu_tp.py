@@ -2,7 +2,9 @@
 each rank keeps its shard of the int8 weights and of the KV pool, the row-split
 projections are followed by one NCCL all-reduce, and the logits must agree with
 the single-GPU run of the same model within 1e-4 (only the summation order of the
-partial sums differs) and with the CPU oracle within 1e-3."""
+partial sums differs) and with the CPU oracle within 1e-3.  The same with the
+exchange done by the library's own kernel over peer memory (NVLink P2P loads,
+arrival flags, residual add folded in) instead of NCCL."""
 import os
 import sys
 
@@ -14,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BLOCK = 16
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, peer):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -22,7 +24,7 @@ def _worker(rank, world, port, out):
     import torch.distributed as dist
     from oracle import pi_oracle as orc
     from paged_infer_b200 import api
-    from paged_infer_b200.tp import exchange_unique_id
+    from paged_infer_b200.tp import enable_peer_exchange, exchange_unique_id
     from test_gpu_model import kv_floats, small_llama
 
     torch.cuda.set_device(rank)
@@ -30,6 +32,8 @@ def _worker(rank, world, port, out):
     try:
         ident = exchange_unique_id(api.nccl_unique_id, dist)
         ctx = api.Context(rank, rank=rank, tp=world, nccl_id=ident)
+        if peer:
+            enable_peer_exchange(ctx, 64 * 512, dist)       # max batch rows x hidden of small_llama
         cfg, om, gm = small_llama(ctx, orc, 9, kv_heads=2)          # 8 heads / 2 KV heads -> one KV head per rank
         rng = np.random.default_rng(9)
         B, nblocks = 6, 8
@@ -65,7 +69,8 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def test_tp2_matches_single_gpu_and_oracle():
+@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer-memory"])
+def test_tp2_matches_single_gpu_and_oracle(peer):
     import torch
     import torch.multiprocessing as mp
 
@@ -74,7 +79,7 @@ def test_tp2_matches_single_gpu_and_oracle():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = 29700 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port + int(peer), out, peer)) for r in range(2)]
     for p in procs:
         p.start()
     res = out.get(timeout=600)
