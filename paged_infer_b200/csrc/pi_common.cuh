@@ -274,7 +274,10 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
 // for all ranks' partials of that slot, adds them in rank order and adds the sum to x.
 bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n);
 float* pi_tp_peer_slot(pi_ctx* ctx);
-pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, size_t n);
+// `emit` (optional): also write the new rows of x as planes (times emit_norm_weight, with the per-chunk sums of
+// squares the consumer turns into 1/rms), so that the projection that follows needs no split kernel.
+pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_act_planes* emit = nullptr,
+                                const float* emit_norm_weight = nullptr, float emit_norm_eps = 0.f);
 
 // ---- device helpers ----------------------------------------------------------------------
 #ifdef __CUDACC__

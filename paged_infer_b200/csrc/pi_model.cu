@@ -291,7 +291,7 @@ pi_status build_model(pi_ctx* ctx, const pi_model_config* cfg, const ModelSource
   if (tp > 1) PI_TRY(alloc_f(ctx, &m->logits_gather, cap * vocab));
   PI_CUDA(ctx, cudaMalloc(&m->tokens_dev, cap * sizeof(uint32_t)));
   PI_CUDA(ctx, cudaMalloc(&m->argmax_dev, cap * sizeof(uint32_t)));
-  if (tp == 1) {
+  {
     PI_CUDA(ctx, cudaMalloc(&m->planes_x, 3 * cap * hidden * sizeof(__nv_bfloat16)));
     PI_CUDA(ctx, cudaMalloc(&m->planes_h, 3 * cap * (size_t)m->inter_local * sizeof(__nv_bfloat16)));
     PI_CUDA(ctx, cudaMalloc(&m->planes_a, 3 * cap * qrows * sizeof(__nv_bfloat16)));
@@ -330,7 +330,8 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
   const size_t qrows = (size_t)m->heads_local * hd, kvrows = (size_t)m->kv_heads_local * hd;
   const size_t qkv_stride = qrows + 2 * kvrows;
   const size_t cap = (size_t)m->capacity;
-  const bool fuse = ctx->opt_fuse_planes && ctx->tp == 1 && m->planes_x && m->planes_h;
+  const bool peer = pi_tp_peer_usable(ctx, (size_t)B * hidden);   // partial sums exchanged through peer memory
+  const bool fuse = ctx->opt_fuse_planes && (ctx->tp == 1 || peer) && m->planes_x && m->planes_h;
   pi_act_planes px, ph, pa;            // residual-stream planes, SwiGLU-output planes, attention-output planes
   px.base = m->planes_x; px.plane_stride = cap * hidden; px.K = hidden;
   px.sumsq = m->sumsq; px.sumsq_stride = cap;
@@ -389,13 +390,13 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     g.epi = PI_EPI_SWIGLU;
     const bool g_tc = fuse && pi_gemm_tc_will_run(ctx, m->gate_up[l], g);
 
-    const bool peer = pi_tp_peer_usable(ctx, (size_t)B * hidden);   // partial sums exchanged through peer memory
     if (ctx->tp > 1) {
       o.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       o.out_stride = hidden;
       PI_TRY(pi_linear_forward(ctx, m->wo[l], o));
-      if (peer) {
-        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, (size_t)B * hidden));
+      if (peer) {   // the exchange kernel adds the residual and hands the new rows on as planes
+        x_ready = g_tc;
+        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, B, hidden, x_ready ? &px : nullptr, m->ffn_norm[l], c.rms_norm_eps));
       } else {
         PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
         PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
@@ -430,9 +431,15 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     if (ctx->tp > 1) {
       d.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       d.out_stride = hidden;
+      if (h_ready) d.in_planes = &ph;
       PI_TRY(pi_linear_forward(ctx, m->down[l], d));
       if (peer) {
-        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, (size_t)B * hidden));
+        const pi_linear* next = l + 1 < L ? m->qkv[l + 1] : (final_x ? m->lm_head : nullptr);
+        pi_linear_args nx;
+        nx.M = B;
+        x_ready = fuse && next && pi_gemm_tc_will_run(ctx, next, nx);
+        PI_TRY(pi_tp_peer_reduce_add(ctx, m->x, B, hidden, x_ready ? &px : nullptr,
+                                     l + 1 < L ? m->attn_norm[l + 1] : m->final_norm, c.rms_norm_eps));
       } else {
         PI_TRY(pi_tp_all_reduce_sum(ctx, m->partial, (size_t)B * hidden));
         PI_TRY(pi_launch_add(ctx, m->x, m->partial, (size_t)B * hidden));
@@ -475,6 +482,7 @@ pi_status project_logits(pi_ctx* ctx, pi_model* m, int first, int rows, const x_
   if (ctx->tp > 1) {
     a.out = m->logits;  // [rows][vocab_local]
     a.out_stride = m->vocab_local;
+    if (xp && xp->valid && first == 0) a.in_planes = &xp->planes;
     PI_TRY(pi_linear_forward(ctx, m->lm_head, a));
     PI_TRY(pi_tp_all_gather(ctx, m->logits, m->logits_gather, (size_t)rows * m->vocab_local * sizeof(float)));
     const size_t total = (size_t)rows * c.vocab_size;

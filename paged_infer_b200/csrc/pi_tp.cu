@@ -122,14 +122,20 @@ constexpr int kPeerMaxTp = 8;
 constexpr uint32_t kPeerSpinLimit = 1u << 22;
 
 struct PeerReduceParams {
-  float* x;
-  size_t n4;                         // float4 count
+  float* x;                          // [rows][cols] residual stream, updated in place
+  int rows, cols;
   int tp, rank, slot;
   const float* data[kPeerMaxTp];     // this slot of every rank
   unsigned long long* flags[kPeerMaxTp];   // flag arrays of every rank
   unsigned long long* epoch;         // local: epoch[slot]
   unsigned int* ticket;              // local: ticket[slot]
   int* err_flag;
+  // optional: the new residual rows as bf16 planes (times a norm weight) + per-chunk sums of squares
+  unsigned short* emit_base;
+  size_t emit_plane_stride;
+  const float* emit_norm;
+  float* emit_sumsq;                 // [chunks per row][emit_sumsq_stride]
+  size_t emit_sumsq_stride;
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
@@ -146,9 +152,12 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {   // never from a
   return v;
 }
 
+constexpr int kPeerChunk = 1024;     // floats of one row handled by one CTA pass (256 threads x float4)
+
 // grid <= number of SMs (all CTAs resident: they all read the epoch before the last one to finish advances it).
 __global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduceParams p) {
   __shared__ int s_ok;
+  __shared__ float s_red[8];
   pi_grid_dependency_wait();          // the partial sums of this rank come from the preceding kernel
   const unsigned long long e = *reinterpret_cast<volatile unsigned long long*>(p.epoch) + 1ull;
   if (blockIdx.x == 0 && threadIdx.x < p.tp && (int)threadIdx.x != p.rank) {
@@ -174,19 +183,52 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduc
   }
   __syncthreads();
   if (s_ok) {
-    float4* x4 = reinterpret_cast<float4*>(p.x);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n4; i += (size_t)gridDim.x * blockDim.x) {
-      float4 part[kPeerMaxTp];
+    const int cpr = (p.cols + kPeerChunk - 1) / kPeerChunk;   // chunks per row
+    for (int chunk = blockIdx.x; chunk < p.rows * cpr; chunk += gridDim.x) {
+      const int row = chunk / cpr, seg = chunk - row * cpr;
+      const int col = seg * kPeerChunk + threadIdx.x * 4;
+      float sq = 0.f;
+      if (col < p.cols) {
+        const size_t off = (size_t)row * p.cols + col;
+        float4 part[kPeerMaxTp];
 #pragma unroll
-      for (int r = 0; r < kPeerMaxTp; ++r)
-        if (r < p.tp) part[r] = (r == p.rank) ? *reinterpret_cast<const float4*>(p.data[r] + 4 * i) : ld_peer_f4(p.data[r] + 4 * i);
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < kPeerMaxTp; ++r)
+          if (r < p.tp) part[r] = (r == p.rank) ? *reinterpret_cast<const float4*>(p.data[r] + off) : ld_peer_f4(p.data[r] + off);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int r = 0; r < kPeerMaxTp; ++r)   // rank order on every rank: all ranks get the same bits
-        if (r < p.tp) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
-      float4 v = x4[i];
-      v.x += sum.x; v.y += sum.y; v.z += sum.z; v.w += sum.w;
-      x4[i] = v;
+        for (int r = 0; r < kPeerMaxTp; ++r)   // rank order on every rank: all ranks get the same bits
+          if (r < p.tp) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
+        float4 v = *reinterpret_cast<float4*>(p.x + off);
+        v.x += sum.x; v.y += sum.y; v.z += sum.z; v.w += sum.w;
+        *reinterpret_cast<float4*>(p.x + off) = v;
+        if (p.emit_base) {
+          float y[4] = {v.x, v.y, v.z, v.w};
+          if (p.emit_norm) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(p.emit_norm + col));
+            y[0] *= w.x; y[1] *= w.y; y[2] *= w.z; y[3] *= w.w;
+          }
+          unsigned short a[4], b[4], c[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) pi_split3(y[j], a[j], b[j], c[j]);
+          unsigned short* q = p.emit_base + off;
+          *reinterpret_cast<uint2*>(q) = make_uint2((uint32_t)a[0] | ((uint32_t)a[1] << 16), (uint32_t)a[2] | ((uint32_t)a[3] << 16));
+          *reinterpret_cast<uint2*>(q + p.emit_plane_stride) = make_uint2((uint32_t)b[0] | ((uint32_t)b[1] << 16), (uint32_t)b[2] | ((uint32_t)b[3] << 16));
+          *reinterpret_cast<uint2*>(q + 2 * p.emit_plane_stride) = make_uint2((uint32_t)c[0] | ((uint32_t)c[1] << 16), (uint32_t)c[2] | ((uint32_t)c[3] << 16));
+          sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        }
+      }
+      if (p.emit_sumsq) {   // sum of squares of this chunk of the row, fixed order
+        sq = pi_warp_sum(sq);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          float t = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) t += s_red[i];
+          p.emit_sumsq[(size_t)seg * p.emit_sumsq_stride + row] = t;
+        }
+        __syncthreads();
+      }
     }
   }
   // the last CTA to finish advances the epoch of this slot for the next exchange on it
@@ -248,14 +290,17 @@ bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n) {
 
 float* pi_tp_peer_slot(pi_ctx* ctx) { return ctx->peer.data[ctx->rank] + (size_t)ctx->peer.next_slot * ctx->peer.slot_floats; }
 
-pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, size_t n) {
-  PI_REQUIRE(ctx, pi_tp_peer_usable(ctx, n) && (uintptr_t)x % 16 == 0, "the peer exchange is not set up for %zu values", n);
+pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_act_planes* emit, const float* emit_norm_weight,
+                                float emit_norm_eps) {
+  const size_t n = (size_t)rows * cols;
+  PI_REQUIRE(ctx, pi_tp_peer_usable(ctx, n) && cols % 4 == 0 && (uintptr_t)x % 16 == 0, "the peer exchange is not set up for %zu values", n);
   pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
   const int slot = ctx->peer.next_slot;
   ctx->peer.next_slot ^= 1;
   PeerReduceParams p = {};
   p.x = x;
-  p.n4 = n / 4;
+  p.rows = rows;
+  p.cols = cols;
   p.tp = ctx->tp;
   p.rank = ctx->rank;
   p.slot = slot;
@@ -267,7 +312,25 @@ pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, size_t n) {
   p.epoch = epoch + slot;
   p.ticket = reinterpret_cast<unsigned int*>(epoch + kPeerSlots) + slot;
   p.err_flag = ctx->dev_err;
-  const unsigned grid = (unsigned)std::min<size_t>((p.n4 + 255) / 256, (size_t)ctx->sm_count);
+  const int cpr = (cols + kPeerChunk - 1) / kPeerChunk;
+  if (emit) {
+    PI_REQUIRE(ctx, emit->base && emit->K == cols && emit->plane_stride % 4 == 0 && (uintptr_t)emit->base % 8 == 0,
+               "planes of %d columns are needed", cols);
+    p.emit_base = reinterpret_cast<unsigned short*>(emit->base);
+    p.emit_plane_stride = emit->plane_stride;
+    p.emit_norm = emit_norm_weight;
+    emit->row_scale = nullptr;
+    emit->sumsq_tiles = 0;
+    if (emit_norm_weight) {
+      PI_REQUIRE(ctx, emit->sumsq && emit->sumsq_stride >= (size_t)rows && (uintptr_t)emit_norm_weight % 16 == 0,
+                 "emit with a norm weight needs a sums-of-squares buffer");
+      p.emit_sumsq = emit->sumsq;
+      p.emit_sumsq_stride = emit->sumsq_stride;
+      emit->sumsq_tiles = cpr;
+      emit->eps = emit_norm_eps;
+    }
+  }
+  const unsigned grid = (unsigned)std::min<size_t>((size_t)rows * cpr, (size_t)ctx->sm_count);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(std::max(grid, 1u));
   cfg.blockDim = dim3(256);
