@@ -47,7 +47,8 @@ TINYLLAMA = dict(hidden_size=2048, num_hidden_layers=22, num_attention_heads=32,
 # traffic of a bench launch = ratio x its algorithmic bytes (traffic grows in proportion to the rows / tokens streamed).
 NCU_TRAFFIC_RATIO = {"gemm_tc": 1.05, "gemv": 1.003, "attention": 1.03}
 GEMV_SHAPES = {"q/o 2048x2048": (2048, 2048), "k/v 256x2048": (256, 2048), "qkv fused 2560x2048": (2560, 2048),
-               "gate/up 5632x2048": (5632, 2048), "down 2048x5632": (2048, 5632), "lm_head 32000x2048": (32000, 2048)}
+               "gate/up 5632x2048": (5632, 2048), "down 2048x5632": (2048, 5632), "lm_head 32000x2048": (32000, 2048),
+               "lm_head Llama-3 128256x4096": (128256, 4096)}
 
 
 # ---- host-side block bookkeeping (what KvCacheManager does for this workload) ---------------------------------
