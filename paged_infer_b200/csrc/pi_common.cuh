@@ -193,6 +193,8 @@ bool pi_gemm_tc_will_run(const pi_ctx* ctx, const pi_linear* lin, const pi_linea
 bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, bool with_norm);
 // True when that launch can also apply the rotary embedding and write K/V into the pool.
 bool pi_gemm_tc_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r);
+// The same for the CUDA-core path (any head_dim that is even).
+bool pi_gemv_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r);
 // The activation split on its own (what the GEMM runs first when it is not given planes): x -> planes in `dst`.
 pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, const float* norm_weight, float eps, int M, int K,
                               pi_act_planes* dst);

@@ -90,7 +90,27 @@ struct GemvParams {
   float eps;
   int use_tma;
   int* err_flag;
+  // optional: rotary embedding + KV write for the fused [q;k;v] projection (rope_hd = 0: off).  The two rows of a
+  // warp's pair are then the two members of a rotation pair, so the finished pair can be rotated in registers.
+  int rope_hd, rope_q_rows, rope_kv_rows, rope_style;
+  const float* rope_cos;
+  const float* rope_sin;
+  float* kv;
+  pi_kv_layout L;
+  int layer;
+  const int32_t* tables;
+  int max_blocks;
+  const int32_t* lens;
+  const int32_t* pos;
 };
+
+// Row r (0 or 1) of row pair `pair`: consecutive rows, or the members of a rotation pair of one head.
+template <bool ROPE>
+__device__ __forceinline__ int gemv_row(const GemvParams& p, int pair, int r) {
+  if (!ROPE) return pair * kRows + r;
+  const int half = p.rope_hd >> 1, head = pair / half, j = pair - head * half;
+  return p.rope_style == 0 ? head * p.rope_hd + j + r * half : head * p.rope_hd + 2 * j + r;
+}
 
 // A lane reads U = EPL/4 consecutive 16-byte units of x per step.  Stored
 // linearly that is a U-way bank conflict for 128-bit shared loads, so unit j of
@@ -103,7 +123,7 @@ __device__ __forceinline__ int unit_swizzle(int group) {
   return 0;
 }
 
-template <typename WT, int MB, int EPI, bool NORM>
+template <typename WT, int MB, int EPI, bool NORM, bool ROPE>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   constexpr int EPL = Widen<WT>::EPL;
   constexpr int U = EPL / 4;
@@ -130,7 +150,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     const unsigned char* rowp[kRows];
 #pragma unroll
     for (int r = 0; r < kRows; ++r)
-      rowp[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)min(pair * kRows + r, p.N - 1) * ld * sizeof(WT);
+      rowp[r] = reinterpret_cast<const unsigned char*>(p.W) + (size_t)min(gemv_row<ROPE>(p, pair, r), p.N - 1) * ld * sizeof(WT);
 #pragma unroll
     for (int t = 0; t < kSteps; ++t) {
       const int k = kg * kGroupElems + t * kStepElems + k_lane;
@@ -298,8 +318,45 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
       float sc[kRows];
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) sc[r] = (p.scales && row0 + r < p.N) ? p.scales[row0 + r] : 1.0f;
-      if (EPI == PI_EPI_SWIGLU) {
+      for (int r = 0; r < kRows; ++r) {
+        const int rw = gemv_row<ROPE>(p, pair, r);
+        sc[r] = (p.scales && rw < p.N) ? p.scales[rw] : 1.0f;
+      }
+      if (ROPE) {
+        // fused [q;k;v] projection: lane m finishes activation row m0+m - rotate the pair (q and k rows), leave q in
+        // `out`, scatter k and v into the pool at the row's position (skipped when the block is not mapped)
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          if (lane == m && m < mcount) {
+            const int gm = m0 + m, hd = p.rope_hd, half = hd >> 1;
+            const int ra = gemv_row<ROPE>(p, pair, 0), rb = gemv_row<ROPE>(p, pair, 1);
+            const int seg = ra < p.rope_q_rows ? 0 : (ra < p.rope_q_rows + p.rope_kv_rows ? 1 : 2);
+            const int within = ra - (seg == 0 ? 0 : (seg == 1 ? p.rope_q_rows : p.rope_q_rows + p.rope_kv_rows));
+            const int position = p.pos[gm];
+            float a = tot[0][m] * sc[0], c = tot[1][m] * sc[1];
+            if (seg < 2) {
+              const int j = pair % half;
+              const float cs = p.rope_cos[(size_t)position * half + j], sn = p.rope_sin[(size_t)position * half + j];
+              const float na = a * cs - c * sn, nc = c * cs + a * sn;
+              a = na;
+              c = nc;
+            }
+            float* o = p.out + (size_t)gm * p.out_stride;
+            o[ra] = a;
+            o[rb] = c;
+            if (seg > 0) {
+              const int lb = position / p.L.block_size, off = position % p.L.block_size;
+              if (lb < p.lens[gm]) {
+                const int pb = p.tables[(size_t)gm * p.max_blocks + lb];
+                const int kh = within / hd, da = within - kh * hd;
+                float* dst = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kh, seg == 2 ? 1 : 0) + (size_t)off * hd;
+                dst[da] = a;
+                dst[da + (rb - ra)] = c;
+              }
+            }
+          }
+        }
+      } else if (EPI == PI_EPI_SWIGLU) {
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
           if (lane == m && m < mcount && row0 + 1 < p.N) {
@@ -333,8 +390,10 @@ template <typename WT, int MB>
 cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, dim3 grid, int threads, size_t smem,
                           bool pdl) {
   void (*k)(const GemvParams) = nullptr;
-#define PI_PICK(E, Nrm) k = gemv_kernel<WT, MB, E, Nrm>
-  if (epi == PI_EPI_STORE) {
+#define PI_PICK(E, Nrm) k = gemv_kernel<WT, MB, E, Nrm, false>
+  if (epi == PI_EPI_STORE && p.rope_hd) {   // fused [q;k;v] projection: own instantiation, the others stay as they are
+    if (norm) k = gemv_kernel<WT, MB, PI_EPI_STORE, true, true>; else k = gemv_kernel<WT, MB, PI_EPI_STORE, false, true>;
+  } else if (epi == PI_EPI_STORE) {
     if (norm) PI_PICK(PI_EPI_STORE, true); else PI_PICK(PI_EPI_STORE, false);
   } else if (epi == PI_EPI_ADD) {
     if (norm) PI_PICK(PI_EPI_ADD, true); else PI_PICK(PI_EPI_ADD, false);
@@ -345,9 +404,10 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
   static size_t granted = 48 * 1024;  // per instantiation of this launcher; attribute calls are slow
   if (smem > granted) {
     // the launcher covers several kernel variants: raise the limit on all of them at once
-    for (auto kk : {gemv_kernel<WT, MB, PI_EPI_STORE, true>, gemv_kernel<WT, MB, PI_EPI_STORE, false>,
-                    gemv_kernel<WT, MB, PI_EPI_ADD, true>, gemv_kernel<WT, MB, PI_EPI_ADD, false>,
-                    gemv_kernel<WT, MB, PI_EPI_SWIGLU, true>, gemv_kernel<WT, MB, PI_EPI_SWIGLU, false>}) {
+    for (auto kk : {gemv_kernel<WT, MB, PI_EPI_STORE, true, false>, gemv_kernel<WT, MB, PI_EPI_STORE, false, false>,
+                    gemv_kernel<WT, MB, PI_EPI_ADD, true, false>, gemv_kernel<WT, MB, PI_EPI_ADD, false, false>,
+                    gemv_kernel<WT, MB, PI_EPI_SWIGLU, true, false>, gemv_kernel<WT, MB, PI_EPI_SWIGLU, false, false>,
+                    gemv_kernel<WT, MB, PI_EPI_STORE, true, true>, gemv_kernel<WT, MB, PI_EPI_STORE, false, true>}) {
       cudaError_t e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
     }
@@ -420,6 +480,15 @@ pi_status pi_launch_quantize(pi_ctx* ctx, const float* w_dev, size_t w_ld, size_
   return PI_OK;
 }
 
+bool pi_gemv_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r) {
+  (void)ctx;
+  if (a.epi != PI_EPI_STORE || a.emit || !r.pool || !r.batch || !r.rope_cos || !r.rope_sin) return false;
+  if (r.head_dim < 2 || (r.head_dim & 1)) return false;               // an odd head_dim leaves one element unpaired
+  if (r.pool->L.head_dim != r.head_dim || r.pool->L.num_kv_heads != r.num_kv_heads) return false;
+  if (lin->rows != (size_t)(r.num_heads + 2 * r.num_kv_heads) * r.head_dim) return false;
+  return r.style == 0 || r.style == 1;
+}
+
 pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
   PI_REQUIRE(ctx, a.M >= 1, "projection batch must be at least 1");
   PI_REQUIRE(ctx, a.epi != PI_EPI_SWIGLU || lin->rows % 2 == 0, "SwiGLU epilogue needs interleaved gate/up rows");
@@ -453,6 +522,24 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
   p.M = a.M;
   p.eps = a.norm_eps;
   p.err_flag = ctx->dev_err;
+  p.rope_hd = 0;
+  if (a.rope) {
+    const pi_rope_kv& r = *a.rope;
+    PI_REQUIRE(ctx, pi_gemv_can_rope(ctx, lin, a, r), "this launch cannot fold the rotary embedding and the KV write in");
+    p.rope_hd = r.head_dim;
+    p.rope_q_rows = r.num_heads * r.head_dim;
+    p.rope_kv_rows = r.num_kv_heads * r.head_dim;
+    p.rope_style = r.style;
+    p.rope_cos = r.rope_cos;
+    p.rope_sin = r.rope_sin;
+    p.kv = r.pool->data;
+    p.L = r.pool->L;
+    p.layer = r.layer;
+    p.tables = r.batch->tables;
+    p.max_blocks = r.batch->max_blocks;
+    p.lens = r.batch->lens;
+    p.pos = r.batch->pos;
+  }
   p.use_tma = ((lin->cols * sizeof(float)) % 16 == 0) && ((uintptr_t)a.x % 16 == 0) &&
               ((a.x_stride * sizeof(float)) % 16 == 0) && ((size_t)mb * lin->cols * sizeof(float) < (1u << 20));
   const bool norm = a.norm_weight != nullptr;

@@ -361,7 +361,8 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     rk.pool = pool;
     rk.layer = l;
     rk.batch = &batch;
-    const bool rope_fused = ctx->opt_fuse_planes && pi_gemm_tc_can_rope(ctx, m->qkv[l], a, rk);
+    const bool rope_fused = ctx->opt_fuse_planes && (pi_gemm_tc_will_run(ctx, m->qkv[l], a) ? pi_gemm_tc_can_rope(ctx, m->qkv[l], a, rk)
+                                                                                             : pi_gemv_can_rope(ctx, m->qkv[l], a, rk));
     if (rope_fused) a.rope = &rk;
     PI_TRY(pi_linear_forward(ctx, m->qkv[l], a));
     x_ready = false;
