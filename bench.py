@@ -92,6 +92,7 @@ class PagedBatch:
             self.tables.append(t)
         for pb in shared:                                   # the cache's own reference
             self.ref[pb] += 1
+        self.packed = None                                  # PackedBlockTables mirror, kept in step by plan()
 
     def _alloc(self) -> int:
         pb = self.free.pop()
@@ -106,16 +107,27 @@ class PagedBatch:
             lb = pos // BLOCK
             if lb >= len(t):
                 t.append(self._alloc())
+                if self.packed is not None:
+                    self.packed.append(b, t[-1])
             elif self.ref[t[lb]] > 1:                       # ensure_writable: copy-on-write split
                 dst = self._alloc()
                 self.cow_copies.append((t[lb], dst))
                 self.ref[t[lb]] -= 1
                 t[lb] = dst
+                if self.packed is not None:
+                    self.packed.remap(b, lb, dst)
         self.total_cow += len(self.cow_copies)
         return self.cow_copies
 
     def commit(self):
         self.lengths = [n + 1 for n in self.lengths]
+
+    def pack(self, api):
+        """The tables as arrays, from now on updated in place by plan() (what an engine's FFI shim would keep)."""
+        self.packed = api.PackedBlockTables(self.batch, max(len(t) for t in self.tables) + 8)
+        for b, t in enumerate(self.tables):
+            self.packed.set_row(b, t)
+        return self.packed
 
     def unique_mapped_tokens(self) -> int:
         """Tokens of KV that one step must read at least once (shared physical blocks count once)."""
@@ -345,6 +357,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
 
     # --- end to end: one public call per step, host bookkeeping + copies inside the timed region -----------------
     pb2 = PagedBatch(2 + rank, B, 2 * (K + W) + 4)
+    pb2.pack(api)
     kv2 = kv  # same pool size and contents distribution; tables index the same physical range
     tok2 = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
     h2d = d2h = 0
@@ -352,7 +365,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     def e2e_step(tok):
         for src, dst in pb2.plan():
             kv2.copy_block(src, dst)
-        ids = model.decode_batch_into(tok, pb2.lengths, pb2.tables, kv2, want_logits=False, want_argmax=True)
+        ids = model.decode_batch_into(tok, pb2.lengths, pb2.packed, kv2, want_logits=False, want_argmax=True)
         pb2.commit()
         return ids
 

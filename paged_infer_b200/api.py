@@ -329,8 +329,46 @@ class BlockTable:
         return len(self.logical_to_physical)
 
 
+class PackedBlockTables:
+    """Block tables of a batch kept as the arrays the library takes: ``mat`` int32 [B, width] (physical ids, -1 =
+    unmapped) and ``lens`` int32 [B].  An engine that appends / remaps single entries as its sequences grow updates
+    these in place instead of flattening Python lists on every step."""
+
+    def __init__(self, batch: int, width: int):
+        self.mat = np.full((batch, max(width, 1)), -1, np.int32)
+        self.lens = np.zeros(batch, np.int32)
+
+    def __len__(self):
+        return self.mat.shape[0]
+
+    def set_row(self, b: int, blocks):
+        n = len(blocks)
+        self._grow(n)
+        self.mat[b, :n] = blocks
+        self.mat[b, n:] = -1
+        self.lens[b] = n
+
+    def append(self, b: int, block: int):
+        n = int(self.lens[b])
+        self._grow(n + 1)
+        self.mat[b, n] = block
+        self.lens[b] = n + 1
+
+    def remap(self, b: int, logical: int, block: int):
+        self.mat[b, logical] = block
+
+    def _grow(self, width: int):
+        if width > self.mat.shape[1]:
+            wider = np.full((self.mat.shape[0], max(width, 2 * self.mat.shape[1])), -1, np.int32)
+            wider[:, :self.mat.shape[1]] = self.mat
+            self.mat = wider
+
+
 def pack_block_tables(tables):
-    """[BlockTable | sequence of ids] -> (int32 [B, max_blocks], int32 lens [B])."""
+    """[BlockTable | sequence of ids] or PackedBlockTables -> (int32 [B, max_blocks], int32 lens [B], max_blocks)."""
+    if isinstance(tables, PackedBlockTables):
+        mb = int(tables.lens.max()) if len(tables) else 0
+        return np.ascontiguousarray(tables.mat[:, :max(mb, 1)]), tables.lens, mb
     rows = [t.logical_to_physical if isinstance(t, BlockTable) else list(t) for t in tables]
     lens = np.array([len(r) for r in rows], np.int32)
     mb = int(lens.max()) if len(rows) and lens.max() > 0 else 0
