@@ -154,8 +154,7 @@ void pi_ctx_destroy(pi_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   pi_tp_destroy(ctx);
-  for (pi_buffer* b : {&ctx->staging_in, &ctx->staging_out, &ctx->attn_tables, &ctx->attn_meta, &ctx->attn_partial,
-                       &ctx->gemm_act, &ctx->gemm_partial})
+  for (pi_buffer* b : {&ctx->staging_in, &ctx->staging_out, &ctx->attn_tables, &ctx->attn_partial, &ctx->gemm_act})
     if (b->ptr) cudaFree(b->ptr);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);

@@ -94,10 +94,9 @@ struct pi_ctx {
 
   // scratch
   pi_buffer staging_in, staging_out;   // device copies of host arguments / results
-  pi_buffer attn_tables, attn_meta;    // block tables + per-entry (len, pos, start)
+  pi_buffer attn_tables;               // block tables + per-entry (len, pos, start)
   pi_buffer attn_partial;              // split-KV partial (m, l, acc)
   pi_buffer gemm_act;                  // bf16 activation planes (+ row factors) for the tensor GEMM
-  pi_buffer gemm_partial;              // split-K partial sums
   void* pinned = nullptr;              // pinned host staging
   size_t pinned_bytes = 0;
 };
