@@ -482,9 +482,19 @@ LLAMA3_8B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
                  intermediate_size=14336, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0)
 
 
+LLAMA2_70B = dict(hidden_size=8192, num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8,
+                  intermediate_size=28672, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0)
+TP_WORKLOADS = {
+    # name: (architecture, model name, batch, contexts: fixed length or (lo, hi) uniform with the given seed)
+    "llama3_8b_tp": (LLAMA3_8B, "Llama-3-8B", 32, 4096, 3),
+    "llama2_70b_tp": (LLAMA2_70B, "Llama-2-70B", 64, (1024, 4096), 4),
+}
+
+
 def run_tp_workload(args, rank: int, world: int, local_rank: int):
-    """`--workload llama3_8b_tp`: Llama-3-8B architecture, int8 projections, batch 32 decode at context 4096,
-    tensor-parallel over all `world` ranks (strong scaling: the total work is fixed)."""
+    """`--workload llama3_8b_tp`: Llama-3-8B architecture, int8 projections, batch 32 decode at context 4096;
+    `--workload llama2_70b_tp`: Llama-2-70B architecture, batch 64, contexts U[1024,4096] (needs >= 2 GPUs).
+    Tensor-parallel over all `world` ranks (strong scaling: the total work is fixed)."""
     import torch
     import torch.distributed as dist
 
@@ -498,8 +508,17 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         ident = exchange_unique_id(api.nccl_unique_id, dist)
     hbm_peak, peak_kind = measured_peaks()
-    cfg = LlamaConfig(**LLAMA3_8B, quantization="int8")
-    B, CTX, K, W = 32, 4096, args.steps, max(args.warmup, 3)
+    arch, model_name, B, ctx_spec, seed = TP_WORKLOADS[args.workload]
+    cfg = LlamaConfig(**arch, quantization="int8")
+    K, W = args.steps, max(args.warmup, 3)
+    rng = np.random.default_rng(seed)
+    if isinstance(ctx_spec, tuple):
+        ctx_len = [int(c) for c in rng.integers(ctx_spec[0], ctx_spec[1] + 1, B)]    # identical on every rank
+        ctx_text = f"U[{ctx_spec[0]},{ctx_spec[1]}] seed {seed}"
+    else:
+        ctx_len = [ctx_spec] * B
+        ctx_text = str(ctx_spec)
+    CTX = max(ctx_len)
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank, tp=world, nccl_id=ident)
@@ -509,14 +528,14 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
         if not args.nccl_exchange:
             enable_peer_exchange(ctx, B * cfg.hidden_size, dist)
             exchange = "peer memory (P2P loads + flags, residual add folded in)"
-    model = api.LlamaWeights.synthetic(ctx, cfg, seed=3, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
-    blocks_per_seq = (CTX + K + W + BLOCK) // BLOCK + 1
-    kv = api.KvCache(ctx, model.kv_layout(B * blocks_per_seq, BLOCK))
+    model = api.LlamaWeights.synthetic(ctx, cfg, seed=seed, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
+    nblk = [(c + K + W + BLOCK) // BLOCK + 1 for c in ctx_len]
+    first = np.concatenate([[0], np.cumsum(nblk)]).astype(int)
+    kv = api.KvCache(ctx, model.kv_layout(int(first[-1]), BLOCK))
     kv.fill_normal(77 + rank, 1.0)
-    tables = [list(range(b * blocks_per_seq, (b + 1) * blocks_per_seq)) for b in range(B)]
-    rng = np.random.default_rng(3)
+    tables = [list(range(int(first[b]), int(first[b + 1]))) for b in range(B)]
     tokens = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)   # identical on every rank
-    pos = [CTX] * B
+    pos = list(ctx_len)
 
     def barrier():
         torch.cuda.synchronize()
@@ -551,16 +570,16 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
     if rank == 0:
         total = sum(v[0] for v in prof.values()) or 1e-9
         weight_bytes = model.weight_bytes()                         # this rank's shard
-        kv_bytes = B * (CTX + W + K // 2) * (cfg.num_key_value_heads // world) * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
+        kv_bytes = sum(c + W + K // 2 for c in ctx_len) * (cfg.num_key_value_heads // world) * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
         step_ms = ms / K
         line = {
-            "metric": "int8 batched paged decode throughput (Llama-3-8B arch, batch 32, context 4096, tensor parallel)",
+            "metric": f"int8 batched paged decode throughput ({model_name} arch, batch {B}, context {ctx_text}, tensor parallel)",
             "value": B * K / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": step_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 weights, f32 activations/accumulate/KV", "data": "synthetic",
-            "config": {"workload": "llama3_8b_tp", "batch": B, "context": CTX, "block_size": BLOCK, "parallelism": f"tp{world}",
+            "config": {"workload": args.workload, "batch": B, "context": ctx_text, "block_size": BLOCK, "parallelism": f"tp{world}",
                        "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if world > 1 else 0, "exchange": exchange,
-                       "weights": "N(0,0.02) generated on device, seed 3", "kv": "N(0,1) fill"},
+                       "weights": f"N(0,0.02) generated on device, seed {seed}", "kv": "N(0,1) fill"},
             "gpu_launches": launches, "clocks": clocks,
             "step_roofline": {"bytes_per_step_per_gpu": weight_bytes + kv_bytes, "weight_bytes_per_gpu": weight_bytes,
                               "kv_bytes_per_gpu": kv_bytes, "achieved_GB/s_per_gpu": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9, 1),
@@ -646,7 +665,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="tinyllama_b64_paged", choices=["tinyllama_b64_paged", "llama3_8b_tp"])
+    ap.add_argument("--workload", default="tinyllama_b64_paged", choices=["tinyllama_b64_paged", "llama3_8b_tp", "llama2_70b_tp"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--nccl-exchange", action="store_true", help="llama3_8b_tp: all-reduce through NCCL instead of the peer-memory kernel")
     args = ap.parse_args()
@@ -663,7 +682,7 @@ def main():
     if args.kernel_case:
         run_kernel_case(args)
         return
-    if args.workload == "llama3_8b_tp":
+    if args.workload in TP_WORKLOADS:
         run_tp_workload(args, rank, world, local_rank)
         return
     run_gpu_arm(args, rank, world, local_rank)
