@@ -89,3 +89,14 @@ def test_loader_reads_the_fixture_and_config(tmp_path):
     p.write_text('{"hidden_size": 64, "num_attention_heads": 8, "rope_theta": 500000.0}')
     c = LlamaConfig.from_hf_config(str(p))
     assert c.hidden_size == 64 and c.num_key_value_heads == 8 and c.rope_theta == 500000.0 and c.vocab_size == 32000
+
+
+def test_rust_ffi_is_generated_from_the_header():
+    """bindings/rust/src/ffi.rs is a pure function of the header: regenerate and compare, and every function is there."""
+    import subprocess
+    import sys
+    gen = os.path.join(ROOT, "bindings", "rust", "gen_ffi.py")
+    assert subprocess.run([sys.executable, gen, "--check"]).returncode == 0, "run python bindings/rust/gen_ffi.py"
+    text = open(os.path.join(ROOT, "bindings", "rust", "src", "ffi.rs")).read()
+    for n in header_functions():
+        assert f"pub fn {n}(" in text, n
