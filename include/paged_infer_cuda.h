@@ -102,7 +102,7 @@ enum { PI_PROF_GEMV = 0, PI_PROF_GEMM_TC = 1, PI_PROF_ATTENTION = 2, PI_PROF_ROP
 pi_status pi_ctx_profile_begin(pi_ctx* ctx);
 pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out /*[PI_PROF_CLASSES]*/, uint64_t* launches_out /*[PI_PROF_CLASSES]*/);
 /* Tuning knobs (all default on): 0/1. */
-enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6 };
+enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6, PI_OPT_ATTN_SHARED = 7 };
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value);
 
 /* ---- quantiser --------------------------------------------------------------- */

@@ -57,7 +57,7 @@ class Context:
         self.device, self.rank, self.tp = device, rank, tp
 
     def close(self):
-        if getattr(self, "handle", None):
+        if getattr(self, "handle", None) and _lib is not None:   # module globals are gone at interpreter exit
             _lib.lib().pi_ctx_destroy(self.handle)
             self.handle = None
 
@@ -213,7 +213,7 @@ class Projection:
         return cls.f32(ctx, np.asarray(bf16_bits, np.uint16))
 
     def close(self):
-        if getattr(self, "handle", None):
+        if getattr(self, "handle", None) and _lib is not None:   # module globals are gone at interpreter exit
             _lib.lib().pi_linear_destroy(self.handle)
             self.handle = None
 
@@ -389,7 +389,7 @@ class KvCache:
         self.handle = h
 
     def close(self):
-        if getattr(self, "handle", None):
+        if getattr(self, "handle", None) and _lib is not None:   # module globals are gone at interpreter exit
             _lib.lib().pi_kv_pool_destroy(self.handle)
             self.handle = None
 
@@ -561,7 +561,7 @@ class LlamaWeights:
         return self
 
     def close(self):
-        if getattr(self, "handle", None):
+        if getattr(self, "handle", None) and _lib is not None:   # module globals are gone at interpreter exit
             _lib.lib().pi_model_destroy(self.handle)
             self.handle = None
 

@@ -209,6 +209,7 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_CUDA_GRAPH: ctx->opt_graph = value != 0; return PI_OK;
     case PI_OPT_PDL: ctx->opt_pdl = value != 0; return PI_OK;
     case PI_OPT_ATTN_TMA: ctx->opt_attn_tma = value; return PI_OK;
+    case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
     case PI_OPT_GEMV_MAX_M:
       PI_REQUIRE(ctx, value >= 1, "gemv max M must be at least 1");

@@ -19,6 +19,8 @@
 // BlockTable::get_physical_location (src/memory/block_table.rs:50-61).
 #include <math.h>
 
+#include <string.h>
+
 #include <algorithm>
 
 #include "pi_common.cuh"
@@ -859,8 +861,12 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
   int32_t* h_start = h_pos + B;
   long total = 0;
   int widest = 0;
+  bool shared = B > 1;
   for (int b = 0; b < B; ++b) {
     const int len = lens_host[b];
+    if (shared && b > 0 &&
+        (len != lens_host[0] || (len > 0 && memcmp(tables_host + (size_t)b * max_blocks, tables_host, (size_t)len * sizeof(int32_t)) != 0)))
+      shared = false;
     PI_REQUIRE(ctx, len >= 0 && len <= max_blocks, "entry %d: table length %d outside [0, %d]", b, len, max_blocks);
     PI_REQUIRE(ctx, pos_host[b] >= 0 && start_host[b] >= 0, "entry %d: negative position", b);
     for (int i = 0; i < mb; ++i) h[(size_t)b * mb + i] = (i < len) ? tables_host[(size_t)b * max_blocks + i] : -1;
@@ -883,6 +889,8 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
   out->B = B;
   out->max_window_blocks = widest;
   out->total_window_blocks = total;
+  out->shared_table = shared;
+  out->shared_len = shared ? lens_host[0] : 0;
   return PI_OK;
 }
 
@@ -920,6 +928,8 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   p.emit_k = 0;
 
   pi_prof_scope prof(ctx, PI_PROF_ATTENTION);
+  if (pi_attention_shared_usable(ctx, pool, num_heads, q, q_stride, out, out_stride, batch))
+    return pi_launch_attention_shared(ctx, pool, layer, num_heads, q, q_stride, out, out_stride, batch);
   const bool fast = (HD == 64 || HD == 128) && (group == 1 || group == 2 || group == 4 || group == 8) &&
                     ((uintptr_t)q % 16 == 0) && (q_stride % 4 == 0);
   cudaError_t e;

@@ -157,3 +157,89 @@ def test_bad_head_grouping_is_an_error(ctx):
         api.PagedAttention(L, 8).run(np.zeros(8 * 4, np.float32), kv, [api.AttnEntry(api.BlockTable([0]), 3)])
     with pytest.raises(api.PiError):  # physical block outside the pool
         api.PagedAttention(L, 6).run(np.zeros(6 * 4, np.float32), kv, [api.AttnEntry(api.BlockTable([9]), 3)])
+
+
+# ---- entries that share one block table (prefill chunks, speculative verify groups) ---------------------------
+
+def shared_table_case(ctx, oracle, hd, H, KH, positions, starts, mapped_blocks, seed, layers=1, layer=0):
+    """All entries map the same table; returns (decode-kernel result, shared-table-kernel result, oracle result)."""
+    from paged_infer_b200 import api
+    n = len(positions)
+    blocks = max(positions) // 16 + 2
+    case = AttnCase(H, KH, hd, 16, 1, blocks, min(mapped_blocks, blocks), num_layers=layers)
+    case.kv_cache = normal_f32(case.kv_cache.size, seed, 1.0)
+    q = normal_f32(n * H * hd, seed + 1, 1.0)
+    tables = [case.tables[0]] * n
+    want = cpu_run(oracle, case, q, tables, positions, starts, layer)
+    ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 0)
+    try:
+        per_entry = gpu_run(ctx, case, q, tables, positions, starts, layer)
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)
+        tiled = gpu_run(ctx, case, q, tables, positions, starts, layer)
+    finally:
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
+    return per_entry, tiled, want
+
+
+@pytest.mark.parametrize("hd,H,KH", [(64, 32, 4), (128, 32, 8), (64, 8, 8), (128, 8, 4), (64, 16, 4)])
+def test_shared_table_chunk_of_consecutive_positions(ctx, oracle, hd, H, KH):
+    """A prefill chunk: 70 consecutive positions (not a multiple of the row tile) starting inside a block, with and
+    without a sliding window, on both layers of a two-layer pool."""
+    pos = list(range(37, 107))
+    for window, layer in ((None, 0), (50, 1), (1, 0)):
+        st = [max(0, p + 1 - window) if window else 0 for p in pos]
+        per_entry, tiled, want = shared_table_case(ctx, oracle, hd, H, KH, pos, st, 99, seed=hd + H + (window or 0), layers=2, layer=layer)
+        close(tiled, want)
+        close(tiled, per_entry)
+
+
+def test_shared_table_long_context_many_tiles(ctx, oracle):
+    """Windows that span many 64-token tiles, chunk at the end of a long context."""
+    pos = list(range(1500, 1628))
+    per_entry, tiled, want = shared_table_case(ctx, oracle, 64, 32, 4, pos, [0] * len(pos), 999, seed=3)
+    close(tiled, want)
+    close(tiled, per_entry)
+    st = [max(0, p - 700) for p in pos]
+    per_entry, tiled, want = shared_table_case(ctx, oracle, 128, 16, 4, pos, st, 999, seed=4)
+    close(tiled, want)
+
+
+def test_shared_table_unmapped_tail_empty_windows_and_scattered_positions(ctx, oracle):
+    """Positions in arbitrary order; blocks past the mapped length score -inf (never read); a window that lies wholly in
+    the unmapped tail or is empty gives zeros, not NaN."""
+    rng = np.random.default_rng(8)
+    pos = [int(p) for p in rng.integers(0, 200, 45)]
+    st = [0] * 45
+    st[3], pos[3] = 50, 49            # empty window
+    st[7], pos[7] = 130, 180          # wholly past the 6 mapped blocks (96 tokens)
+    st[11], pos[11] = 90, 120         # straddles the end of the mapping
+    per_entry, tiled, want = shared_table_case(ctx, oracle, 64, 8, 2, pos, st, 6, seed=5)
+    assert np.all(np.isfinite(tiled))
+    close(tiled, want)
+    close(tiled, per_entry)
+    assert np.all(tiled[3] == 0.0) and np.all(tiled[7] == 0.0)
+    # nothing mapped at all
+    per_entry, tiled, want = shared_table_case(ctx, oracle, 64, 8, 2, pos, st, 0, seed=6)
+    assert np.all(tiled == 0.0)
+
+
+def test_shared_table_pool_garbage_outside_the_windows_is_never_used(ctx, oracle):
+    """Slots past the highest position hold NaN (a block that was handed out but not filled yet): the result must not
+    change, because those slots are neither scored nor multiplied."""
+    from paged_infer_b200 import api
+    hd, H, KH = 64, 32, 4
+    pos = list(range(3, 75))
+    case = AttnCase(H, KH, hd, 16, 1, 6, 6)
+    case.kv_cache = normal_f32(case.kv_cache.size, 21, 1.0)
+    q = normal_f32(len(pos) * H * hd, 22, 1.0)
+    tables = [case.tables[0]] * len(pos)
+    want = cpu_run(oracle, case, q, tables, pos, [0] * len(pos))
+    kv = case.kv_cache.reshape(1, case.total_blocks, 16, KH, 2, hd)
+    kv[0, case.tables[0][4], 11:, :, :, :] = np.nan     # tokens 75.. of the sequence
+    kv[0, case.tables[0][5]] = np.nan
+    ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)
+    try:
+        got = gpu_run(ctx, case, q, tables, pos, [0] * len(pos))
+    finally:
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
+    close(got, want)

@@ -187,3 +187,39 @@ def test_two_layers_hand_planes_across_the_layer_boundary(ctx, oracle):
     finally:
         ctx.set_option(api._lib.PI_OPT_FUSE_PLANES, 1)
     assert np.abs(fused - plain).max() < 1e-4
+
+
+@pytest.mark.parametrize("arch", ["tinyllama", "llama3"])
+def test_large_prefill_chunks_use_the_shared_table_attention(ctx, oracle, arch):
+    """Prefill in chunks of 256 positions: the chunk's attention runs in the shared-table kernel (all positions of a
+    chunk map one table); logits of the last position and the KV written on the way against the oracle."""
+    from paged_infer_b200 import api
+    if arch == "tinyllama":
+        cfg, om, gm = wide_llama(ctx, oracle, 41, hidden=2048, heads=32, kv_heads=4, inter=5632, vocab=32000, theta=10000.0,
+                                 max_batch=256)
+    else:
+        cfg, om, gm = wide_llama(ctx, oracle, 42, hidden=4096, heads=32, kv_heads=8, inter=14336, vocab=4096, theta=500000.0,
+                                 max_batch=256)
+    n, nblocks = 300, 24
+    rng = np.random.default_rng(17)
+    prompt = rng.integers(0, cfg.vocab_size, n).astype(np.uint32)
+    table = [int(b) for b in rng.permutation(nblocks)[:n // BLOCK + 1]]
+    okv = np.zeros(kv_floats(cfg, nblocks), np.float32)
+    want = om.prefill_batched(prompt, 0, table, okv, BLOCK, 32)
+    gkv = api.KvCache(ctx, gm.kv_layout(nblocks, BLOCK))
+    gkv.upload(np.zeros_like(okv))
+    ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)
+    try:
+        got, tok = gm.prefill_batched(prompt, 0, table, gkv, 256, want_argmax=True)
+    finally:
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
+    assert np.abs(got - want).max() < 1e-3 and tok == oracle.argmax(want)
+    assert np.abs(gkv.download() - okv).max() < 1e-4
+    # and the same prompt through the per-entry decode kernel gives the same logits
+    gkv.upload(np.zeros_like(okv))
+    ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 0)
+    try:
+        plain = gm.prefill_batched(prompt, 0, table, gkv, 256)
+    finally:
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
+    assert np.abs(got - plain).max() < 1e-4
