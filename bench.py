@@ -389,7 +389,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
 
     # --- dominant kernel alone (rank 0) ----------------------------------------------------------------------------
     roof = other = gemv = cpu = profile_shares = None
-    batch1 = None
+    batch1 = prefill = None
     if rank == 0:
         H, hd, KH, NL = cfg.num_attention_heads, cfg.head_dim, cfg.num_key_value_heads, cfg.num_hidden_layers
         # Every launch of P real decode steps bracketed by CUDA events on the launching stream.
@@ -411,14 +411,19 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
             ms, n = prof[cls]
             if n == 0:
                 continue
-            us = ms * 1e3 / n
+            us_serial = ms * 1e3 / n
+            # inside the timed region launches overlap their predecessor's tail (programmatic dependent launch); the
+            # events that bracket every launch here serialise them.  Duration inside the step = this class's share
+            # of the bracketed device time x the step time of the timed region / its launches per step.
+            us = (ms / total_ms) * (resident_ms / K) * 1e3 / (n / P)
             rl[cls] = {"kernel": names[cls], "bound": "hbm", "achieved": round(algo[cls] / us / 1e3, 1), "peak": hbm_peak,
                        "unit": "GB/s", "frac": round(algo[cls] / us / 1e3 / hbm_peak, 3),
                        "traffic": int(NCU_TRAFFIC_RATIO[cls] * algo[cls]),
                        "traffic_source": f"ncu dram bytes of a single-kernel capture scaled by algorithmic bytes (x{NCU_TRAFFIC_RATIO[cls]})",
-                       "us_per_launch": round(us, 2), "launches_per_step": n / P, "algorithmic_bytes_per_launch": int(algo[cls]),
+                       "us_per_launch": round(us, 2), "us_per_launch_bracketed": round(us_serial, 2), "launches_per_step": n / P, "algorithmic_bytes_per_launch": int(algo[cls]),
                        "share_of_step_device_time": round(ms / total_ms, 3), "peak_kind": f"of {peak_kind}",
-                       "timing": f"CUDA events around each of {n} launches inside {P} decode steps"}
+                       "timing": f"CUDA events around each of {n} launches inside {P} decode steps give the class's share; "
+                                 "x the CUDA-event step time of the timed region / launches per step"}
         order = sorted(rl, key=lambda c: -rl[c]["share_of_step_device_time"])
         roof = rl[order[0]] if order else None
         other = [rl[c] for c in order[1:]]
@@ -439,6 +444,30 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         bytes1 = weight_bytes + (128 + 64 + 1) * KH * 2 * hd * 4 * NL
         batch1 = {"tok/s": round(1e3 / ms1, 1), "ms_per_step": round(ms1, 4), "roofline_tok/s": round(hbm_peak * 1e9 / bytes1, 1),
                   "frac_of_hbm_roofline": round((bytes1 / (ms1 / 1e3)) / (hbm_peak * 1e9), 3), "bytes_per_step": bytes1}
+
+        # prefill (config 0: 128-token prompt; config 4 style: 2048-token prompt), a model instance with room for
+        # 512-position chunks; the chunk's attention runs in the shared-table kernel from 256 positions on
+        prefill = {}
+        pmodel = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=512, max_positions=4096)
+        for n_prompt, chunk in ((128, 128), (2048, 512)):
+            nbp = n_prompt // BLOCK + 1
+            kvp = api.KvCache(ctx, pmodel.kv_layout(nbp, BLOCK))
+            prompt = np.random.default_rng(7).integers(0, cfg.vocab_size, n_prompt).astype(np.uint32)
+            tab = list(range(nbp))
+            pmodel.prefill_batched(prompt, 0, tab, kvp, chunk)
+            torch.cuda.synchronize()
+            reps = 3
+            e0.record()
+            for _ in range(reps):
+                pmodel.prefill_batched(prompt, 0, tab, kvp, chunk)
+            e1.record()
+            torch.cuda.synchronize()
+            msp = e0.elapsed_time(e1) / reps
+            flops = 2.0 * n_prompt * (weight_bytes - cfg.vocab_size * cfg.hidden_size) + 4.0 * NL * H * hd * n_prompt * (n_prompt + 1) / 2
+            prefill[f"prompt{n_prompt}_chunk{chunk}"] = {"tok/s": round(n_prompt / (msp / 1e3), 1), "ms": round(msp, 3),
+                                                        "useful_TFLOP/s": round(flops / (msp / 1e3) / 1e12, 1)}
+            kvp.close()
+        pmodel.close()
 
         if world == 1 and not args.no_cpu:
             pbc = PagedBatch(2, B, 16)
@@ -470,7 +499,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                               "kv_tokens_unique": kv_tokens_unique, "kv_tokens_logical": kv_tokens_logical,
                               "achieved_GB/s": round(step_bytes / (step_ms / 1e3) / 1e9, 1), "peak_GB/s": hbm_peak,
                               "frac": round(step_bytes / (step_ms / 1e3) / 1e9 / hbm_peak, 3), "peak_kind": f"of {peak_kind}"},
-            "gemv_m1": gemv, "batch1_decode": batch1, "cpu_baseline": cpu,
+            "gemv_m1": gemv, "batch1_decode": batch1, "prefill": prefill, "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -647,6 +676,33 @@ def run_kernel_case(args):
         e1.record()
         torch.cuda.synchronize()
         algo = B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 + 2 * qv.numel() * 4
+    elif case == "attention_prefill":
+        # the last 512-position chunk of a 2048-token prompt: every entry maps the same table
+        cfg = LlamaConfig(**TINYLLAMA, quantization="int8")
+        n_ctx, chunk = 2048, 512
+        nblk = n_ctx // BLOCK
+        layout = api.KvLayout(1, nblk, BLOCK, cfg.num_key_value_heads, cfg.head_dim)
+        kv = api.KvCache(ctx, layout)
+        kv.fill_normal(9, 1.0)
+        attn = api.PagedAttention(layout, cfg.num_attention_heads)
+        qv = torch.randn(chunk, cfg.num_attention_heads * cfg.head_dim, device="cuda", dtype=torch.float32)
+        ov = torch.empty_like(qv)
+        table = api.BlockTable(list(range(nblk)))
+        entries = [api.AttnEntry(table, n_ctx - chunk + i) for i in range(chunk)]
+        attn.run_device(qv, ov, kv, entries)
+        torch.cuda.synchronize()
+        e0.record()
+        for r in range(reps):
+            attn.run_device(qv, ov, kv, entries)
+        e1.record()
+        torch.cuda.synchronize()
+        pairs = sum(n_ctx - chunk + i + 1 for i in range(chunk))          # (position, token) pairs inside the windows
+        flops = 4.0 * pairs * cfg.num_attention_heads * cfg.head_dim
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        print(json.dumps({"kernel_case": case, "launch_groups": reps, "us_per_launch_group": round(us, 2), "useful_flops": flops,
+                          "useful_TFLOP/s": round(flops / us / 1e6, 2), "tensor_TFLOP/s_issued": round(3 * flops / us / 1e6, 2),
+                          "note": "each product runs as three TF32 MMAs (exact hi/lo split)"}), flush=True)
+        return
     else:
         raise SystemExit(f"unknown kernel case {case}")
     us = e0.elapsed_time(e1) * 1e3 / reps
@@ -659,7 +715,7 @@ def run_kernel_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel-case", default=None,
-                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention"],
+                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention", "attention_prefill"],
                     help="run a few launches of one kernel on a small case (for a profiler) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
