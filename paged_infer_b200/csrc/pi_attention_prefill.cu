@@ -361,6 +361,11 @@ bool pi_attention_shared_usable(const pi_ctx* ctx, const pi_kv_pool* pool, int n
   const size_t smem = (size_t)(2 * kRows + 4 * kTile) * (HD + 4) * sizeof(float);
   if (smem + 1024 > ctx->smem_optin) return false;
   if (ctx->opt_attn_shared >= 2) return true;
+  if (pi_attention_shared_tc_usable(ctx, pool, num_heads, q, q_stride, out, out_stride)) {
+    // tcgen05 kernel: 128 rows per CTA; worth it from about a quarter of the SMs on
+    const long ctas_tc = (long)L.num_kv_heads * (((long)batch.B * group + 127) / 128);
+    return ctas_tc * 4 >= ctx->sm_count;
+  }
   const long ctas = (long)L.num_kv_heads * ((batch.B + kRows / group - 1) / (kRows / group));
   return ctas * 4 >= (long)ctx->sm_count * 3;   // measured: break-even near 3/4 of the SMs, 1.3-2x faster from one CTA per SM on
 }
@@ -369,6 +374,9 @@ pi_status pi_launch_attention_shared(pi_ctx* ctx, const pi_kv_pool* pool, int la
                                      size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch) {
   const pi_kv_layout& L = pool->L;
   const int HD = L.head_dim, group = num_heads / L.num_kv_heads;
+  // head_dim 64: the tcgen05 kernel (opt_attn_shared 3 keeps this mma.sync kernel, for comparison)
+  if (ctx->opt_attn_shared != 3 && pi_attention_shared_tc_usable(ctx, pool, num_heads, q, q_stride, out, out_stride))
+    return pi_launch_attention_shared_tc(ctx, pool, layer, num_heads, q, q_stride, out, out_stride, batch);
   SharedAttnParams p;
   p.q = q;
   p.q_stride = q_stride;

@@ -83,7 +83,7 @@ struct pi_ctx {
   bool opt_graph = true;
   bool opt_pdl = true;
   int opt_gemv_max_m = 4;
-  int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always
+  int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always, 3 always and on the mma.sync kernel
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
   int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 
@@ -242,6 +242,10 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
 // bf16 planes (row factor 1) for the projection that follows; *emitted tells whether it did.
 bool pi_attention_shared_usable(const pi_ctx* ctx, const pi_kv_pool* pool, int num_heads, const float* q, size_t q_stride,
                                 const float* out, size_t out_stride, const pi_attn_batch& batch);
+bool pi_attention_shared_tc_usable(const pi_ctx* ctx, const pi_kv_pool* pool, int num_heads, const float* q, size_t q_stride,
+                                   const float* out, size_t out_stride);
+pi_status pi_launch_attention_shared_tc(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
+                                        size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
 pi_status pi_launch_attention_shared(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
                                      size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
 pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,

@@ -174,7 +174,10 @@ def shared_table_case(ctx, oracle, hd, H, KH, positions, starts, mapped_blocks, 
     ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 0)
     try:
         per_entry = gpu_run(ctx, case, q, tables, positions, starts, layer)
-        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 3)      # the mma.sync kernel
+        legacy = gpu_run(ctx, case, q, tables, positions, starts, layer)
+        close(legacy, want)
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)      # head_dim 64: the tcgen05 kernel
         tiled = gpu_run(ctx, case, q, tables, positions, starts, layer)
     finally:
         ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
@@ -237,9 +240,10 @@ def test_shared_table_pool_garbage_outside_the_windows_is_never_used(ctx, oracle
     kv = case.kv_cache.reshape(1, case.total_blocks, 16, KH, 2, hd)
     kv[0, case.tables[0][4], 11:, :, :, :] = np.nan     # tokens 75.. of the sequence
     kv[0, case.tables[0][5]] = np.nan
-    ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 2)
-    try:
-        got = gpu_run(ctx, case, q, tables, pos, [0] * len(pos))
-    finally:
-        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
-    close(got, want)
+    for opt in (2, 3):
+        ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, opt)
+        try:
+            got = gpu_run(ctx, case, q, tables, pos, [0] * len(pos))
+        finally:
+            ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
+        close(got, want)
