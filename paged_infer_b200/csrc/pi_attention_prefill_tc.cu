@@ -298,22 +298,29 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_shared_tc_kernel(const TcA
       unsigned mapped = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) mapped |= (block_of(jt * 4 + i) >= 0 ? 1u : 0u) << i;
-      float mx = -INFINITY;
+      // a tile that lies wholly inside the window of every row of the warp needs no masks
+      const bool inside = mapped == 0xFu && jt * kTileTc >= st_r && jt * kTileTc + kTileTc - 1 <= pos_r;
+      if (!__all_sync(0xffffffffu, inside)) {
 #pragma unroll
-      for (int i = 0; i < kTileTc; ++i) {
-        const int t = jt * kTileTc + i;
-        const bool ok = ((mapped >> (i >> 4)) & 1u) && t >= st_r && t <= pos_r;
-        s[i] = ok ? s[i] : -INFINITY;
-        mx = fmaxf(mx, s[i]);
+        for (int i = 0; i < kTileTc; ++i) {
+          const int t = jt * kTileTc + i;
+          const bool ok = ((mapped >> (i >> 4)) & 1u) && t >= st_r && t <= pos_r;
+          s[i] = ok ? s[i] : -INFINITY;
+        }
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64 links
+#pragma unroll
+      for (int i = 0; i < kTileTc; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_run, mx);
       const float corr = (m_run == -INFINITY) ? 1.f : ex2a(m_run - m_new);
-      float psum = 0.f;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < kTileTc; ++i) {
         s[i] = (s[i] == -INFINITY) ? 0.f : ex2a(s[i] - m_new);
-        psum += s[i];
+        ps4[i & 3] += s[i];
       }
+      const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l_run = l_run * corr + psum;
       m_run = m_new;
       // the previous tile's output is ready by now (its MMAs were issued when its P was handed over): fold it in and
