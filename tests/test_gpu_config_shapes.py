@@ -223,3 +223,33 @@ def test_large_prefill_chunks_use_the_shared_table_attention(ctx, oracle, arch):
     finally:
         ctx.set_option(api._lib.PI_OPT_ATTN_SHARED, 1)
     assert np.abs(got - plain).max() < 1e-4
+
+
+def test_config0_full_size_prefill_128_then_128_greedy_steps(ctx, oracle):
+    """The batch-1 benchmark configuration at FULL size: TinyLlama-1.1B architecture (22 layers, hidden 2048, 32/4 heads
+    of 64, FFN 5632, vocab 32000), weights N(0, 0.02) quantised by the reference scheme, prompt of 128 uniform token
+    ids, chunked prefill, then 128 greedy decode steps (teacher forced, so one flip could not cascade): logits within
+    1e-3 of the oracle's int8 CPU path at every step and zero greedy mismatches."""
+    from paged_infer_b200 import api
+    cfg, om, gm = wide_llama(ctx, oracle, 0, hidden=2048, heads=32, kv_heads=4, inter=5632, vocab=32000, theta=10000.0,
+                             layers=22, max_batch=32)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab_size, 128).astype(np.uint32)
+    nblocks = 17
+    table = [int(b) for b in rng.permutation(nblocks + 3)[:nblocks]]
+    okv = np.zeros(kv_floats(cfg, nblocks + 3), np.float32)
+    gkv = api.KvCache(ctx, gm.kv_layout(nblocks + 3, BLOCK))
+    gkv.upload(okv)
+    want = om.prefill_batched(prompt, 0, table, okv, BLOCK, 32)
+    got, tok = gm.prefill_batched(prompt, 0, table, gkv, 32, want_argmax=True)
+    worst = float(np.abs(got - want).max())
+    mism = int(tok != oracle.argmax(want))
+    nxt = oracle.argmax(want)
+    for step in range(128):
+        pos = 128 + step
+        want = om.forward(nxt, pos, table, okv, BLOCK)
+        got, ids = gm.decode_batch_into([nxt], [pos], [table], gkv, want_argmax=True)
+        worst = max(worst, float(np.abs(got[0] - want).max()))
+        mism += int(ids[0] != oracle.argmax(want))
+        nxt = oracle.argmax(want)
+    assert worst < 1e-3 and mism == 0, (worst, mism)
