@@ -7,23 +7,23 @@
 // One CTA owns 128 query rows - (position, query head) pairs of one KV head, one row per TMEM lane - and walks the
 // window in tiles of 64 tokens.  Every f32 value x is carried as three bf16 planes x0 + x1 + x2 = x (exact), and a
 // product of two split values keeps the six terms down to 2^-24:  a0 b0 + (a0 b1 + a1 b0) + (a0 b2 + a1 b1 + a2 b0).
-// The planes of the streaming operand are stacked along the MMA's N axis, so these are three MMAs per K step:
-//     A = a0, B = [b0; b1; b2] (N = 192)  ->  accumulator columns 0..191
-//     A = a1, B = [b0; b1]     (N = 128)  ->  accumulator columns 0..127
-//     A = a2, B = [b0]         (N =  64)  ->  accumulator columns 0..63
-// and the result is the sum of the three 64-column groups (a * b0, (a0 + a1) * b1, a0 * b2).  Every product of two
-// bf16 is exact in the f32 accumulator, so each group is an f32 dot product of its terms.
+// These are six MMAs (M = 128, N = 64, K = 16) per K step, one per plane pair (i, j) with i + j <= 2, smallest terms
+// first, all into the SAME 64 accumulator columns: every product of two bf16 is exact in the f32 accumulator, so the
+// columns hold an f32 dot product of the terms and the softmax threads read 64 columns per tile.
 //
 //   scores  S = Q K^T : A = the planes of Q (tensor memory, written once), B = the planes of the K tile
 //                       (shared memory, K-major, 128-byte swizzle, rows = tokens)
-//   output  O = P V   : A = the planes of P (tensor memory, written by the softmax threads over the score columns
-//                       they have just read), B = the planes of V^T (rows = head dims, K = tokens)
+//   output  O = P V   : A = the planes of P (tensor memory, written by the softmax threads, two buffers),
+//                       B = the planes of V^T (rows = head dims, K = tokens); the product of one tile lands in scratch
+//                       columns and is folded into the running output with the online-softmax correction
 //
 // Warp roles: 0-3 = one thread per query row (read S, mask, online softmax in the log2 domain, write P, read the
-// tile's O and fold it into the running f32 output held in registers); 4-7 = converters (read the next K/V tile
-// from the pool, split into planes, store swizzled: K as is, V transposed; one tile ahead of the MMAs);
-// 8 = TMEM allocation and the MMA issuer.  Hand-offs go through mbarriers; every wait is bounded and raises the
-// context's error word instead of hanging.
+// tile's O and fold it into the running f32 output held in registers); 4-7 = converters (request the next K/V tile
+// from the pool, split the current one into planes, store swizzled: K as is, V transposed; up to four tiles ahead
+// of the MMAs); 8 = TMEM allocation and the MMA issuer (the scores of tile j+1 are issued before the output product
+// of tile j, so they run while the row threads work on tile j).  Hand-offs go through mbarriers; every wait is
+// bounded and raises the context's error word instead of hanging.  Measured and dropped: two threads per row with
+// the row maximum exchanged through shared memory (the extra hand-off per tile cost more than the halved work).
 #include <math.h>
 
 #include <algorithm>
