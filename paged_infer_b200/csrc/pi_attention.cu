@@ -952,6 +952,12 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
     nsplit = 64;
     bpc = (batch.max_window_blocks + nsplit - 1) / nsplit;
   }
+  // Windows of up to 32 blocks whose merge kernel would have nothing else to do (no planes to emit): one CTA per
+  // (kv head, entry) walks the whole window and writes the output itself - one launch less per layer.
+  if (!(emit && emit->base) && batch.max_window_blocks <= 32) {
+    nsplit = 1;
+    bpc = (std::max(batch.max_window_blocks, 1) + kAttnWarps - 1) / kAttnWarps * kAttnWarps;
+  }
   p.blocks_per_cta = bpc;
   p.nsplit = nsplit;
   if (nsplit > 1) {
