@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Regenerate the golden fixtures in this directory from the reference.
 
-Runs only where the reference checkout is mounted (``PAGED_INFER_REFERENCE``,
-default ``/root/reference``).  It imports the reference's own NumPy generator
+Runs only where a checkout of the reference is at hand: pass its directory as the
+first argument or in ``PAGED_INFER_REFERENCE``.  It imports the reference's own NumPy generator
 ``scripts/gen_golden_fixture.py`` (an independent transcription of HuggingFace
 ``modeling_llama``), calls its ``build_weights`` / ``reference_forward`` with
 the seed it uses (20240517) and writes
@@ -25,12 +25,12 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("PAGED_INFER_REFERENCE", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PAGED_INFER_REFERENCE", "")
 
 
 def main() -> int:
     gen_path = os.path.join(REF, "scripts", "gen_golden_fixture.py")
-    if not os.path.exists(gen_path):
+    if not REF or not os.path.exists(gen_path):
         print(f"reference generator not found at {gen_path}", file=sys.stderr)
         return 1
     sys.dont_write_bytecode = True
