@@ -782,11 +782,11 @@ cudaError_t launch_fast(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p) 
 template <int HD, int G, int STAGES>
 cudaError_t launch_tma_one(pi_ctx* ctx, dim3 grid, const AttnParams& p, size_t smem) {
   auto k = attn_decode_tma_kernel<HD, G, STAGES>;
-  static size_t granted = 0;  // per instantiation: the attribute call is slow, so raise the limit only when needed
-  if (smem > granted) {
+  static pi_smem_grant granted;  // per instantiation: the attribute call is slow, so raise the limit only when needed
+  if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    granted = smem;
+    granted.of(ctx) = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
@@ -804,11 +804,11 @@ cudaError_t launch_tma_one(pi_ctx* ctx, dim3 grid, const AttnParams& p, size_t s
 template <int HD, int G, int STAGES>
 cudaError_t launch_v3_one(pi_ctx* ctx, dim3 grid, const AttnParams& p, size_t smem) {
   auto k = attn_decode_v3_kernel<HD, G, STAGES>;
-  static size_t granted = 0;
-  if (smem > granted) {
+  static pi_smem_grant granted;
+  if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    granted = smem;
+    granted.of(ctx) = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

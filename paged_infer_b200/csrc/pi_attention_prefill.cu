@@ -316,11 +316,11 @@ template <int HD, int G>
 cudaError_t launch_one(pi_ctx* ctx, dim3 grid, const SharedAttnParams& p) {
   auto k = attn_shared_table_kernel<HD, G>;
   constexpr size_t smem = (size_t)(2 * kRows + 4 * kTile) * (HD + 4) * sizeof(float);
-  static bool granted = false;
-  if (!granted) {
+  static pi_smem_grant granted;
+  if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    granted = true;
+    granted.of(ctx) = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

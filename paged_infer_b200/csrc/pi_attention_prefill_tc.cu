@@ -505,11 +505,11 @@ pi_status pi_launch_attention_shared_tc(pi_ctx* ctx, const pi_kv_pool* pool, int
   p.err_flag = ctx->dev_err;
   // At least 120 KB of shared memory per CTA: two of these CTAs (each wants all 512 TMEM columns) never share an SM.
   const size_t smem = std::max(kSmemTc, (size_t)120 * 1024);
-  static bool granted = false;
-  if (!granted) {
+  static pi_smem_grant granted;
+  if (smem > granted.of(ctx)) {
     const cudaError_t e = cudaFuncSetAttribute(attn_shared_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "shared-table attention: %s", cudaGetErrorString(e));
-    granted = true;
+    granted.of(ctx) = smem;
   }
   const int ppc = kRowsTc / p.group;
   cudaLaunchConfig_t cfg = {};

@@ -292,6 +292,13 @@ pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_ac
                                 const float* emit_norm_weight = nullptr, float emit_norm_eps = 0.f);
 
 // ---- device helpers ----------------------------------------------------------------------
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per device and slow: what each launcher has already been granted,
+// per device of the calling context.
+struct pi_smem_grant {
+  size_t bytes[64] = {};
+  size_t& of(const pi_ctx* ctx) { return bytes[(unsigned)ctx->device & 63u]; }
+};
+
 #ifdef __CUDACC__
 // y = p0 + p1 + p2 exactly, each a bf16 (each remainder has at most 16, then 8 significant bits left).
 __device__ __forceinline__ void pi_split3(float y, unsigned short& p0, unsigned short& p1, unsigned short& p2) {

@@ -688,11 +688,11 @@ template <int BN, int STAGES>
 cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, dim3 grid) {
   constexpr size_t smem = std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + 1024, kMinSmem);
   auto k = gemm_ta_kernel<BN, STAGES>;
-  static bool granted = false;  // per instantiation
-  if (!granted) {
+  static pi_smem_grant granted;  // per instantiation
+  if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    granted = true;
+    granted.of(ctx) = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

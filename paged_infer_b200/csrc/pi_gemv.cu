@@ -401,8 +401,8 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
     if (norm) PI_PICK(PI_EPI_SWIGLU, true); else PI_PICK(PI_EPI_SWIGLU, false);
   }
 #undef PI_PICK
-  static size_t granted = 48 * 1024;  // per instantiation of this launcher; attribute calls are slow
-  if (smem > granted) {
+  static pi_smem_grant granted;  // per instantiation of this launcher; attribute calls are slow
+  if (smem > std::max(granted.of(ctx), (size_t)48 * 1024)) {
     // the launcher covers several kernel variants: raise the limit on all of them at once
     for (auto kk : {gemv_kernel<WT, MB, PI_EPI_STORE, true, false>, gemv_kernel<WT, MB, PI_EPI_STORE, false, false>,
                     gemv_kernel<WT, MB, PI_EPI_ADD, true, false>, gemv_kernel<WT, MB, PI_EPI_ADD, false, false>,
@@ -411,7 +411,7 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
       cudaError_t e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
     }
-    granted = smem;
+    granted.of(ctx) = smem;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
