@@ -26,6 +26,7 @@ namespace {
 
 constexpr int kRows = 2;    // output rows per warp pass
 constexpr int kSteps = 4;   // 512-byte steps of a row per load group
+constexpr int kSplitWarps = 3;   // warps that share a row pair when a matrix has few, long rows
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -123,7 +124,9 @@ __device__ __forceinline__ int unit_swizzle(int group) {
   return 0;
 }
 
-template <typename WT, int MB, int EPI, bool NORM, bool ROPE>
+// KS > 1 (matrices with few, long rows): KS consecutive warps share a row pair, warp ks of them takes the K groups
+// ks, ks + KS, ...; the partial sums meet in shared memory and are added in warp order by the first warp of the set.
+template <typename WT, int MB, int EPI, bool NORM, bool ROPE, int KS = 1>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   constexpr int EPL = Widen<WT>::EPL;
   constexpr int U = EPL / 4;
@@ -158,9 +161,13 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
       for (int r = 0; r < kRows; ++r) g[t][r] = (k < ld) ? ld_stream_16(rowp[r] + (size_t)k * sizeof(WT)) : make_int4(0, 0, 0, 0);
     }
   };
-  int pair = blockIdx.x * nwarps + warp, kg = 0;
+  __shared__ float part[2][KS > 1 ? 8 : 1][kRows][MB];   // KS > 1: partial sums of the warps of a set (two parities)
+  const int ks = KS > 1 ? warp % KS : 0;
+  const int pair_stride = KS > 1 ? total_warps / KS : total_warps;
+  int pair = KS > 1 ? (blockIdx.x * nwarps + warp) / KS : blockIdx.x * nwarps + warp, kg = ks;
+  int n_done = 0;
   // the first group does not depend on the producer kernel: request it before waiting for the activations
-  if (pair < npairs) load_group(wcur, pair, 0);
+  if (pair < npairs) load_group(wcur, pair, kg);
 
   pi_grid_dependency_wait();
 
@@ -273,10 +280,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 
   const int s = unit_swizzle<U>(lane);
   while (pair < npairs) {
-    int npair = pair, nkg = kg + 1;
-    if (nkg == ngroups) {
-      nkg = 0;
-      npair = pair + total_warps;
+    int npair = pair, nkg = kg + KS;
+    if (nkg >= ngroups) {
+      nkg = ks;
+      npair = pair + pair_stride;
     }
     if (npair < npairs) load_group(wnxt, npair, nkg);
 
@@ -306,7 +313,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
       }
     }
 
-    if (kg == ngroups - 1) {  // the row pair is complete: reduce, apply the scale, write
+    if (kg + KS >= ngroups) {  // this warp's share of the row pair is complete: reduce, apply the scale, write
       const int row0 = pair * kRows;
       float tot[kRows][MB];
 #pragma unroll
@@ -316,6 +323,33 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
           tot[r][m] = pi_warp_sum(acc[r][m].x + acc[r][m].y);
           acc[r][m] = make_float2(0.f, 0.f);
         }
+      bool writer = true;
+      if (KS > 1) {
+        // the warps of the set meet at their own named barrier (they walk the same row pairs, so they arrive the same
+        // number of times); the first warp adds the partial sums in warp order
+        const int par = n_done & 1;
+        ++n_done;
+        if (lane == 0) {
+#pragma unroll
+          for (int r = 0; r < kRows; ++r)
+#pragma unroll
+            for (int m = 0; m < MB; ++m) part[par][warp][r][m] = tot[r][m];
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + warp / KS), "r"(KS * 32) : "memory");
+        writer = ks == 0;
+        if (writer) {
+#pragma unroll
+          for (int r = 0; r < kRows; ++r)
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+              float t = part[par][warp][r][m];
+#pragma unroll
+              for (int j = 1; j < KS; ++j) t += part[par][warp + j][r][m];
+              tot[r][m] = t;
+            }
+        }
+      }
+      if (writer) {
       float sc[kRows];
 #pragma unroll
       for (int r = 0; r < kRows; ++r) {
@@ -376,6 +410,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             }
           }
       }
+      }  // writer
     }
 #pragma unroll
     for (int t = 0; t < kSteps; ++t)
@@ -388,10 +423,13 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 
 template <typename WT, int MB>
 cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, dim3 grid, int threads, size_t smem,
-                          bool pdl) {
+                          bool pdl, int ksplit) {
   void (*k)(const GemvParams) = nullptr;
 #define PI_PICK(E, Nrm) k = gemv_kernel<WT, MB, E, Nrm, false>
-  if (epi == PI_EPI_STORE && p.rope_hd) {   // fused [q;k;v] projection: own instantiation, the others stay as they are
+  if (ksplit == kSplitWarps) {   // few long rows (pi_launch_gemv asks for it only without norm, rotary embedding, SwiGLU)
+    if (epi == PI_EPI_ADD) k = gemv_kernel<WT, MB, PI_EPI_ADD, false, false, kSplitWarps>;
+    else k = gemv_kernel<WT, MB, PI_EPI_STORE, false, false, kSplitWarps>;
+  } else if (epi == PI_EPI_STORE && p.rope_hd) {   // fused [q;k;v] projection: own instantiation, the others stay as they are
     if (norm) k = gemv_kernel<WT, MB, PI_EPI_STORE, true, true>; else k = gemv_kernel<WT, MB, PI_EPI_STORE, false, true>;
   } else if (epi == PI_EPI_STORE) {
     if (norm) PI_PICK(PI_EPI_STORE, true); else PI_PICK(PI_EPI_STORE, false);
@@ -407,7 +445,9 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
     for (auto kk : {gemv_kernel<WT, MB, PI_EPI_STORE, true, false>, gemv_kernel<WT, MB, PI_EPI_STORE, false, false>,
                     gemv_kernel<WT, MB, PI_EPI_ADD, true, false>, gemv_kernel<WT, MB, PI_EPI_ADD, false, false>,
                     gemv_kernel<WT, MB, PI_EPI_SWIGLU, true, false>, gemv_kernel<WT, MB, PI_EPI_SWIGLU, false, false>,
-                    gemv_kernel<WT, MB, PI_EPI_STORE, true, true>, gemv_kernel<WT, MB, PI_EPI_STORE, false, true>}) {
+                    gemv_kernel<WT, MB, PI_EPI_STORE, true, true>, gemv_kernel<WT, MB, PI_EPI_STORE, false, true>,
+                    gemv_kernel<WT, MB, PI_EPI_ADD, false, false, kSplitWarps>,
+                    gemv_kernel<WT, MB, PI_EPI_STORE, false, false, kSplitWarps>}) {
       cudaError_t e = cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
     }
@@ -428,11 +468,11 @@ cudaError_t launch_gemv_t(pi_ctx* ctx, const GemvParams& p, int epi, bool norm, 
 
 template <typename WT>
 cudaError_t launch_gemv_w(pi_ctx* ctx, const GemvParams& p, int mb, int epi, bool norm, dim3 grid, int threads,
-                          size_t smem, bool pdl) {
+                          size_t smem, bool pdl, int ksplit) {
   switch (mb) {
-    case 1: return launch_gemv_t<WT, 1>(ctx, p, epi, norm, grid, threads, smem, pdl);
-    case 2: return launch_gemv_t<WT, 2>(ctx, p, epi, norm, grid, threads, smem, pdl);
-    default: return launch_gemv_t<WT, 4>(ctx, p, epi, norm, grid, threads, smem, pdl);
+    case 1: return launch_gemv_t<WT, 1>(ctx, p, epi, norm, grid, threads, smem, pdl, ksplit);
+    case 2: return launch_gemv_t<WT, 2>(ctx, p, epi, norm, grid, threads, smem, pdl, ksplit);
+    default: return launch_gemv_t<WT, 4>(ctx, p, epi, norm, grid, threads, smem, pdl, ksplit);
   }
 }
 
@@ -505,7 +545,18 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
   const size_t max_ctas = std::max<size_t>(1, (size_t)ctx->sm_count * 2 / mtiles);
   int warps = 8;
   while (warps > 1 && (npairs + warps - 1) / warps < max_ctas) warps >>= 1;
-  const size_t ctas = std::min<size_t>((npairs + warps - 1) / warps, max_ctas);
+  size_t ctas = std::min<size_t>((npairs + warps - 1) / warps, max_ctas);
+  // Few rows of at least three 2 KiB groups each, with no prologue or pairing to keep (the down projection of a small
+  // model): at most half the warps of the grid would find a row pair, each walking its groups one after the other.
+  // Sets of three warps share a row pair instead: three times the loads in flight.
+  int ksplit = 1;
+  const size_t row_bytes = lin->ld * (lin->kind == PI_INT8 ? 1 : lin->kind == PI_BF16 ? 2 : 4);
+  if (!a.norm_weight && !a.rope && a.epi != PI_EPI_SWIGLU && row_bytes > (size_t)(kSplitWarps - 1) * kSteps * 512 &&
+      npairs * 2 <= max_ctas * 8) {
+    ksplit = kSplitWarps;
+    warps = 2 * kSplitWarps;
+    ctas = std::min<size_t>((npairs + 1) / 2, max_ctas);
+  }
   dim3 grid((unsigned)ctas, (unsigned)mtiles);
 
   GemvParams p;
@@ -546,11 +597,11 @@ pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args
   pi_prof_scope prof(ctx, PI_PROF_GEMV);
   cudaError_t e;
   if (lin->kind == PI_INT8)
-    e = launch_gemv_w<int8_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+    e = launch_gemv_w<int8_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl, ksplit);
   else if (lin->kind == PI_BF16)
-    e = launch_gemv_w<uint16_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+    e = launch_gemv_w<uint16_t>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl, ksplit);
   else
-    e = launch_gemv_w<float>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl);
+    e = launch_gemv_w<float>(ctx, p, mb, a.epi, norm, grid, warps * 32, smem, ctx->opt_pdl, ksplit);
   if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(e));
   ctx->launches++;
   return PI_OK;
