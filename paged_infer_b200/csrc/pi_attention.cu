@@ -952,9 +952,10 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
     nsplit = 64;
     bpc = (batch.max_window_blocks + nsplit - 1) / nsplit;
   }
-  // Windows of up to 32 blocks whose merge kernel would have nothing else to do (no planes to emit): one CTA per
-  // (kv head, entry) walks the whole window and writes the output itself - one launch less per layer.
-  if (!(emit && emit->base) && batch.max_window_blocks <= 32) {
+  // Windows of up to 12 blocks whose merge kernel would have nothing else to do (no planes to emit): one CTA per
+  // (kv head, entry) walks the whole window and writes the output itself - one launch less per layer (measured at
+  // batch 1: faster up to about 190 tokens of context, slower from 300 on).
+  if (!(emit && emit->base) && batch.max_window_blocks <= 12) {
     nsplit = 1;
     bpc = (std::max(batch.max_window_blocks, 1) + kAttnWarps - 1) / kAttnWarps * kAttnWarps;
   }
