@@ -136,7 +136,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   float* xs = reinterpret_cast<float*>(smem_raw);  // [MB][ld]
   __shared__ __align__(8) unsigned long long mbar;
   __shared__ float red[MB][8];
-  __shared__ float inv_norm[MB];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int ld = (int)p.ld, K = p.K;
@@ -215,29 +214,14 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     __syncthreads();
   }
 
-  // ---- optional RMSNorm: mean of squares per activation row -----------------
-  if (NORM) {
-#pragma unroll
-    for (int m = 0; m < MB; ++m) {
-      float ss = 0.f;
-      for (int k = tid; k < K; k += blockDim.x) {
-        const float v = xs[(size_t)m * ld + k];
-        ss = fmaf(v, v, ss);
-      }
-      ss = pi_warp_sum(ss);
-      if (lane == 0) red[m][warp] = ss;
-    }
-    __syncthreads();
-    if (tid < MB) {
-      float ss = 0.f;
-      for (int w = 0; w < nwarps; ++w) ss += red[tid][w];
-      inv_norm[tid] = 1.0f / sqrtf(ss / (float)K + p.eps);
-    }
-    __syncthreads();
-  }
-  // ---- in-place pass per EPL-float group: scale by the norm and swizzle units -
+  // ---- in-place pass per EPL-float group: swizzle units; with RMSNorm (math::rms_norm, src/math.rs:4-22) also
+  // multiply by the norm weight and collect the sum of squares.  The row factor 1/rms is applied to the finished
+  // dot products in the epilogue (one pass and two barriers less than normalising x first).
   {
     const int groups = ld / EPL;
+    float ssm[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) ssm[m] = 0.f;
     for (int idx = tid; idx < groups * MB; idx += blockDim.x) {
       const int m = idx / groups, g = idx - m * groups;
       float4* base = reinterpret_cast<float4*>(xs + (size_t)m * ld + (size_t)g * EPL);
@@ -245,7 +229,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
       for (int j = 0; j < U; ++j) u[j] = base[j];
       if (NORM) {
-        const float inv = inv_norm[m];
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          sq = fmaf(u[j].x, u[j].x, sq);
+          sq = fmaf(u[j].y, u[j].y, sq);
+          sq = fmaf(u[j].z, u[j].z, sq);
+          sq = fmaf(u[j].w, u[j].w, sq);
+        }
+#pragma unroll
+        for (int mm = 0; mm < MB; ++mm) ssm[mm] += (mm == m) ? sq : 0.f;
         const float4* nw = reinterpret_cast<const float4*>(p.norm_weight + (size_t)g * EPL);
 #pragma unroll
         for (int j = 0; j < U; ++j) {
@@ -257,18 +250,32 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             w4.z = kk + 2 < K ? p.norm_weight[kk + 2] : 0.f;
             w4.w = 0.f;
           }
-          u[j].x = u[j].x * inv * w4.x;
-          u[j].y = u[j].y * inv * w4.y;
-          u[j].z = u[j].z * inv * w4.z;
-          u[j].w = u[j].w * inv * w4.w;
+          u[j].x *= w4.x;
+          u[j].y *= w4.y;
+          u[j].z *= w4.z;
+          u[j].w *= w4.w;
         }
       }
       const int s = unit_swizzle<U>(g & 31);
 #pragma unroll
       for (int j = 0; j < U; ++j) base[j ^ s] = u[j];
     }
+    if (NORM) {
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        const float ss = pi_warp_sum(ssm[m]);
+        if (lane == 0) red[m][warp] = ss;
+      }
+    }
     __syncthreads();
   }
+  // 1/rms of activation row m, from the warps' partial sums in warp order (every thread gets the same bits)
+  auto row_factor = [&](int m) -> float {
+    if (!NORM) return 1.0f;
+    float ss = 0.f;
+    for (int w = 0; w < nwarps; ++w) ss += red[m][w];
+    return 1.0f / sqrtf(ss / (float)K + p.eps);
+  };
   pi_grid_launch_dependents();
 
   // ---- stream the weight rows -------------------------------------------------
@@ -367,7 +374,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             const int seg = ra < p.rope_q_rows ? 0 : (ra < p.rope_q_rows + p.rope_kv_rows ? 1 : 2);
             const int within = ra - (seg == 0 ? 0 : (seg == 1 ? p.rope_q_rows : p.rope_q_rows + p.rope_kv_rows));
             const int position = p.pos[gm];
-            float a = tot[0][m] * sc[0], c = tot[1][m] * sc[1];
+            const float rf = row_factor(m);
+            float a = tot[0][m] * sc[0] * rf, c = tot[1][m] * sc[1] * rf;
             if (seg < 2) {
               const int j = pair % half;
               const float cs = p.rope_cos[(size_t)position * half + j], sn = p.rope_sin[(size_t)position * half + j];
@@ -394,7 +402,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
           if (lane == m && m < mcount && row0 + 1 < p.N) {
-            const float g = tot[0][m] * sc[0], u = tot[1][m] * sc[1];
+            const float rf = row_factor(m);
+            const float g = tot[0][m] * sc[0] * rf, u = tot[1][m] * sc[1] * rf;
             p.out[(size_t)(m0 + m) * p.out_stride + (row0 >> 1)] = (g / (1.0f + expf(-g))) * u;
           }
         }
@@ -405,7 +414,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
           for (int m = 0; m < MB; ++m) {
             if (lane == r * MB + m && m < mcount && row0 + r < p.N) {
               float* o = p.out + (size_t)(m0 + m) * p.out_stride + row0 + r;
-              const float v = tot[r][m] * sc[r];
+              const float v = tot[r][m] * sc[r] * row_factor(m);
               *o = (EPI == PI_EPI_ADD) ? (*o + v) : v;
             }
           }
