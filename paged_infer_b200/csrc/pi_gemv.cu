@@ -170,6 +170,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 
   pi_grid_dependency_wait();
 
+  // fused [q;k;v] projection: lane m finishes activation row m0+m; its position and the physical block that takes its
+  // K and V are looked up now, off the path between the dot products and the stores
+  int my_pos = 0, my_pb = -1;
+  if (ROPE && lane < mcount) {
+    const int gm = m0 + lane;
+    my_pos = p.pos[gm];
+    const int lb = my_pos / p.L.block_size;
+    if (lb < p.lens[gm]) my_pb = p.tables[(size_t)gm * p.max_blocks + lb];
+  }
+
   // ---- stage x[m0 .. m0+mcount) into shared memory, once per CTA ---------------------------------
   bool landed = false;
   if (p.use_tma) {
@@ -293,6 +303,19 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
       npair = pair + pair_stride;
     }
     if (npair < npairs) load_group(wnxt, npair, nkg);
+    // residual add: the value this lane will add to is requested before the arithmetic of the pair's last group
+    float old_out = 0.f;
+    if (EPI == PI_EPI_ADD && !ROPE && ks == 0 && kg + KS >= ngroups) {
+      const int r = lane / MB, m = lane - r * MB;
+      if (r < kRows && m < mcount && pair * kRows + r < p.N)
+        old_out = p.out[(size_t)(m0 + m) * p.out_stride + pair * kRows + r];
+    }
+    float rp_cs = 1.f, rp_sn = 0.f;   // rotation of this pair at lane m's position, requested likewise
+    if (ROPE && lane < mcount && kg + KS >= ngroups) {
+      const int half = p.rope_hd >> 1;
+      rp_cs = p.rope_cos[(size_t)my_pos * half + pair % half];
+      rp_sn = p.rope_sin[(size_t)my_pos * half + pair % half];
+    }
 
     const int kbase = kg * kGroupElems;
 #pragma unroll
@@ -369,17 +392,14 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
           if (lane == m && m < mcount) {
-            const int gm = m0 + m, hd = p.rope_hd, half = hd >> 1;
+            const int gm = m0 + m, hd = p.rope_hd;
             const int ra = gemv_row<ROPE>(p, pair, 0), rb = gemv_row<ROPE>(p, pair, 1);
             const int seg = ra < p.rope_q_rows ? 0 : (ra < p.rope_q_rows + p.rope_kv_rows ? 1 : 2);
             const int within = ra - (seg == 0 ? 0 : (seg == 1 ? p.rope_q_rows : p.rope_q_rows + p.rope_kv_rows));
-            const int position = p.pos[gm];
             const float rf = row_factor(m);
             float a = tot[0][m] * sc[0] * rf, c = tot[1][m] * sc[1] * rf;
             if (seg < 2) {
-              const int j = pair % half;
-              const float cs = p.rope_cos[(size_t)position * half + j], sn = p.rope_sin[(size_t)position * half + j];
-              const float na = a * cs - c * sn, nc = c * cs + a * sn;
+              const float na = a * rp_cs - c * rp_sn, nc = c * rp_cs + a * rp_sn;
               a = na;
               c = nc;
             }
@@ -387,9 +407,9 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             o[ra] = a;
             o[rb] = c;
             if (seg > 0) {
-              const int lb = position / p.L.block_size, off = position % p.L.block_size;
-              if (lb < p.lens[gm]) {
-                const int pb = p.tables[(size_t)gm * p.max_blocks + lb];
+              const int off = my_pos % p.L.block_size;
+              if (my_pb >= 0) {   // an unmapped position: the write is skipped silently
+                const int pb = my_pb;
                 const int kh = within / hd, da = within - kh * hd;
                 float* dst = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kh, seg == 2 ? 1 : 0) + (size_t)off * hd;
                 dst[da] = a;
@@ -415,7 +435,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             if (lane == r * MB + m && m < mcount && row0 + r < p.N) {
               float* o = p.out + (size_t)(m0 + m) * p.out_stride + row0 + r;
               const float v = tot[r][m] * sc[r] * row_factor(m);
-              *o = (EPI == PI_EPI_ADD) ? (*o + v) : v;
+              *o = (EPI == PI_EPI_ADD) ? (old_out + v) : v;
             }
           }
       }
