@@ -310,6 +310,14 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
       if (r < kRows && m < mcount && pair * kRows + r < p.N)
         old_out = p.out[(size_t)(m0 + m) * p.out_stride + pair * kRows + r];
     }
+    float sc[kRows] = {1.0f, 1.0f};   // the rows' scales, requested likewise
+    if (kg + KS >= ngroups && ks == 0) {
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const int rw = gemv_row<ROPE>(p, pair, r);
+        if (p.scales && rw < p.N) sc[r] = p.scales[rw];
+      }
+    }
     float rp_cs = 1.f, rp_sn = 0.f;   // rotation of this pair at lane m's position, requested likewise
     if (ROPE && lane < mcount && kg + KS >= ngroups) {
       const int half = p.rope_hd >> 1;
@@ -380,12 +388,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
       }
       if (writer) {
-      float sc[kRows];
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const int rw = gemv_row<ROPE>(p, pair, r);
-        sc[r] = (p.scales && rw < p.N) ? p.scales[rw] : 1.0f;
-      }
       if (ROPE) {
         // fused [q;k;v] projection: lane m finishes activation row m0+m - rotate the pair (q and k rows), leave q in
         // `out`, scatter k and v into the pool at the row's position (skipped when the block is not mapped)
