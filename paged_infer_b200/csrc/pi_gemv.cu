@@ -167,6 +167,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   int n_done = 0;
   // the first group does not depend on the producer kernel: request it before waiting for the activations
   if (pair < npairs) load_group(wcur, pair, kg);
+  // so does the norm weight of the group this thread will scale first (K a multiple of 4: no ragged tail)
+  float4 nw_pre[U];
+  const bool nw_pre_ok = NORM && (K & 3) == 0;
+  if (nw_pre_ok) {
+    const int groups = ld / EPL, g = tid % groups;
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+      nw_pre[j] = (tid < groups * MB && g * EPL + 4 * j < K) ? __ldg(reinterpret_cast<const float4*>(p.norm_weight + (size_t)g * EPL) + j)
+                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 
   pi_grid_dependency_wait();
 
@@ -253,7 +263,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int j = 0; j < U; ++j) {
           const int kk = g * EPL + 4 * j;
-          float4 w4 = (kk + 3 < K) ? nw[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 w4 = (nw_pre_ok && idx == tid) ? nw_pre[j] : (kk + 3 < K) ? nw[j] : make_float4(0.f, 0.f, 0.f, 0.f);
           if (kk < K && kk + 3 >= K) {  // ragged tail of the norm weight
             w4.x = p.norm_weight[kk];
             w4.y = kk + 1 < K ? p.norm_weight[kk + 1] : 0.f;
