@@ -669,6 +669,10 @@ static __global__ void advance_kernel(uint32_t* tokens, const uint32_t* chosen, 
     pos[b] = p;
     start[b] = window < 0 ? 0 : max(0, p + 1 - window);
   }
+  if (gridDim.x == 1) {   // a single block: it bumps the step counter itself once all its threads have read it
+    __syncthreads();
+    if (threadIdx.x == 0) *step_counter = step + 1;
+  }
 }
 
 // Bumps the step counter once all blocks of advance_kernel are done (stream order).
@@ -684,12 +688,25 @@ static pi_status decode_one_step(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, con
   PI_TRY(project_logits(ctx, m, 0, B, &xs));
   PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
-  advance_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(m->tokens_dev, m->argmax_dev, history, step_counter,
-                                                           const_cast<int32_t*>(batch.pos), const_cast<int32_t*>(batch.start),
-                                                           m->cfg.attention_window, B);
-  PI_CHECK_LAUNCH(ctx);
-  next_step_kernel<<<1, 1, 0, ctx->stream>>>(step_counter);
-  PI_CHECK_LAUNCH(ctx);
+  const int blocks = (B + 127) / 128;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(128);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, advance_kernel, m->tokens_dev, (const uint32_t*)m->argmax_dev, history, step_counter,
+                                           const_cast<int32_t*>(batch.pos), const_cast<int32_t*>(batch.start),
+                                           m->cfg.attention_window, B);
+  if (e != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "advance launch failed: %s", cudaGetErrorString(e));
+  ctx->launches++;
+  if (blocks > 1) {   // several blocks read the counter: it moves on in a launch of its own
+    next_step_kernel<<<1, 1, 0, ctx->stream>>>(step_counter);
+    PI_CHECK_LAUNCH(ctx);
+  }
   return PI_OK;
 }
 
