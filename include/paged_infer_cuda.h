@@ -74,6 +74,8 @@ pi_status pi_ctx_create(int device, void* stream, pi_ctx** out);
  * projections keep the matching column slice and are followed by one
  * all-reduce.  No counterpart in the reference (it has no multi-device code). */
 pi_status pi_nccl_unique_id(void* out_128_bytes);
+/* nccl_unique_id may be NULL: the context then has no NCCL communicator and only the peer-memory exchange below
+ * works (the vocab-split LM head's all-gather, which needs NCCL, fails with PI_ERR_NCCL). */
 pi_status pi_ctx_create_tp(int device, void* stream, int rank, int tp,
                            const void* nccl_unique_id, pi_ctx** out);
 /* Optional peer-memory path for the exchange after the row-split projections (o, down): instead of an NCCL
@@ -86,6 +88,20 @@ pi_status pi_ctx_create_tp(int device, void* stream, int rank, int tp,
 #define PI_TP_PEER_HANDLE_BYTES 64
 pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* handle_out_64_bytes);
 pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles_tp_times_64_bytes);
+/* The same set-up for a host that drives all GPUs from ONE process (the reference engine is a single process,
+ * src/bin/http_server.rs:143-266): a process cannot open IPC handles of its own allocations, so it passes the base
+ * pointer of every rank's buffer instead (pi_tp_peer_base of that rank's context after pi_tp_peer_export, in rank
+ * order; the host has enabled peer access between the devices).  No counterpart in the reference. */
+void* pi_tp_peer_base(const pi_ctx* ctx);
+pi_status pi_tp_peer_import_pointers(pi_ctx* ctx, void* const* bases_tp);
+/* The exchange on its own: x_dev[rows x cols] += sum over all ranks of partial_dev[rows x cols] (the partial sums of
+ * a row-split projection), added in rank order so that every rank ends with the same bits.  Peer-memory path when
+ * it is set up, NCCL all-reduce otherwise.  Every rank must call it with the same shape.  After a
+ * PI_ERR_TIMEOUT the ranks' slots are out of step: the peer path is disabled for the context and later
+ * exchanges use NCCL.  Ranks must enter each exchange within the wait budget of their peers (about a second by
+ * default, PI_OPT_PEER_SPIN_LIMIT) and must synchronise on the host (a barrier) before any of them destroys its
+ * context, because peers read its buffer directly.  No counterpart in the reference. */
+pi_status pi_tp_exchange_add(pi_ctx* ctx, const float* partial_dev, float* x_dev, int rows, int cols);
 void pi_ctx_destroy(pi_ctx* ctx);
 /* Block until everything queued on the context's stream has finished. */
 pi_status pi_ctx_synchronize(pi_ctx* ctx);
@@ -101,8 +117,9 @@ enum { PI_PROF_GEMV = 0, PI_PROF_GEMM_TC = 1, PI_PROF_ATTENTION = 2, PI_PROF_ROP
        PI_PROF_COLLECTIVE = 5, PI_PROF_CLASSES = 6 };
 pi_status pi_ctx_profile_begin(pi_ctx* ctx);
 pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out /*[PI_PROF_CLASSES]*/, uint64_t* launches_out /*[PI_PROF_CLASSES]*/);
-/* Tuning knobs (all default on): 0/1. */
-enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6, PI_OPT_ATTN_SHARED = 7 };
+/* Tuning knobs (the 0/1 ones default on). */
+enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6, PI_OPT_ATTN_SHARED = 7,
+       PI_OPT_PEER_SPIN_LIMIT = 8 /* polls, 64 ns apart, that a rank waits for a peer's partial sums; 0 = default */ };
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value);
 
 /* ---- quantiser --------------------------------------------------------------- */
@@ -284,6 +301,9 @@ pi_status pi_model_create_synthetic(pi_ctx* ctx, const pi_model_config* cfg, uin
 void pi_model_destroy(pi_model* model);
 /* Replaces: LlamaWeights::weight_bytes (src/model.rs:587-603), bytes on this device. */
 size_t pi_model_weight_bytes(const pi_model* model);
+/* Rows one batched forward can take (the max_batch the model was created with).
+ * Replaces: BatchScratch::capacity (src/model.rs:540-572). */
+int pi_model_max_batch(const pi_model* model);
 
 /* Advance B sequences by one token each.  tokens[b] lands at positions[b] of
  * the sequence with block table row b; its K/V are written to the pool (skipped
@@ -296,6 +316,16 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* model, pi_kv_pool* pool,
                                 const uint32_t* tokens_host, const int32_t* positions_host,
                                 const int32_t* block_tables_host, int max_blocks, const int32_t* table_lens_host,
                                 int B, float* logits_host_or_null, uint32_t* argmax_host_or_null);
+
+/* pi_model_decode_batch with the logits of SOME rows only: argmax_host receives all B greedy ids, and
+ * logits_host receives n_logit_rows x vocab floats, row i being the logits of batch row logit_rows_host[i]
+ * (for the sequences the host samples itself, temperature > 0; greedy ones need only their id).
+ * Replaces: the per-sequence read of BatchScratch::logits_for_mut in Engine::run_groups (src/engine.rs:742-755). */
+pi_status pi_model_decode_batch_rows(pi_ctx* ctx, pi_model* model, pi_kv_pool* pool,
+                                     const uint32_t* tokens_host, const int32_t* positions_host,
+                                     const int32_t* block_tables_host, int max_blocks, const int32_t* table_lens_host,
+                                     int B, const int32_t* logit_rows_host, int n_logit_rows,
+                                     float* logits_host, uint32_t* argmax_host);
 
 /* Consume n prompt tokens of one sequence starting at start_pos, `chunk`
  * positions per pass, and return the logits of the last position only.

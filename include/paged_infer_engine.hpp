@@ -24,7 +24,8 @@ namespace pi {
 struct EngineConfig {
   size_t block_size = 16;
   size_t num_blocks = 256;
-  size_t max_batch_size = 64;        // live sequences per step
+  size_t max_batch_size = 64;        // rows of one batched forward (BatchScratch capacity, src/engine.rs:210); more live
+                                     // sequences than this are advanced in several passes per step
   size_t prefill_chunk_size = 32;
   uint32_t eos_token = 0xFFFFFFFFu;
   bool prefix_cache = true;
@@ -62,6 +63,10 @@ class Engine {
   Engine(pi_ctx* ctx, pi_model* model, const pi_kv_layout& layout_one_block, const EngineConfig& cfg)
       : ctx_(ctx), model_(model), cfg_(cfg), kv_(cfg.num_blocks, cfg.block_size) {
     kv_.with_prefix_cache(cfg.prefix_cache);
+    if (cfg_.max_batch_size == 0) throw EngineError("max_batch_size must be at least 1");
+    // one batched forward never exceeds what the model's scratch was built for
+    const int cap = pi_model_max_batch(model_);
+    if (cap > 0 && (size_t)cap < cfg_.max_batch_size) cfg_.max_batch_size = (size_t)cap;
     pi_kv_layout L = layout_one_block;
     L.num_blocks = (int)cfg.num_blocks;
     L.block_size = (int)cfg.block_size;
@@ -118,7 +123,12 @@ class Engine {
   }
 
   void admit() {
-    while (!waiting_.empty() && active_.size() + waiting_.front().num_samples <= cfg_.max_batch_size) {
+    // Memory is the only gate, as in the reference (src/engine.rs:496-503): a request is admitted as soon as the pool
+    // can house its prompt; the number of live sequences is not limited here (decode() advances them in passes).
+    // All samples of one request are decoded greedily and therefore identical; the reference gives such requests a
+    // temperature of 0.8 (src/engine.rs:543-551), and sampling beyond argmax stays with the host
+    // (pi_model_decode_batch_rows hands back the logits of the sequences that need it).
+    while (!waiting_.empty()) {
       const Request& req = waiting_.front();
       const size_t seq_id = next_seq_++;
       auto adm = kv_.admit(seq_id, req.tokens, tick_);
@@ -190,29 +200,32 @@ class Engine {
     }
     if (run.empty()) return;
 
-    const int B = (int)run.size();
-    size_t max_blocks = 1;
-    for (size_t idx : run) max_blocks = std::max(max_blocks, active_[idx].table.len());
-    std::vector<uint32_t> tokens(B), chosen(B);
-    std::vector<int32_t> positions(B), lens(B), tables((size_t)B * max_blocks, -1);
-    for (int b = 0; b < B; ++b) {
-      const Sequence& s = active_[run[b]];
-      tokens[b] = s.token_ids.back();
-      positions[b] = (int32_t)(s.token_ids.size() - 1);
-      lens[b] = (int32_t)s.table.len();
-      for (size_t i = 0; i < s.table.len(); ++i) tables[(size_t)b * max_blocks + i] = s.table.slots()[i].block;
-    }
-    check(pi_model_decode_batch(ctx_, model_, pool_, tokens.data(), positions.data(), tables.data(), (int)max_blocks, lens.data(), B,
-                                nullptr, chosen.data()),
-          "pi_model_decode_batch");
-    ++stats_.decode_batches;
-    for (int b = 0; b < B; ++b) {   // commit
-      Sequence& s = active_[run[b]];
-      s.token_ids.push_back(chosen[b]);
-      s.generated.push_back(chosen[b]);
-      ++stats_.generated_tokens;
-      if (chosen[b] == cfg_.eos_token) s.finished = FinishReason::Eos;
-      else if (s.generated.size() >= s.max_tokens) s.finished = FinishReason::Length;
+    // passes of at most max_batch_size rows, like run_groups (src/engine.rs:722-760)
+    for (size_t start = 0; start < run.size(); start += cfg_.max_batch_size) {
+      const int B = (int)std::min(cfg_.max_batch_size, run.size() - start);
+      size_t max_blocks = 1;
+      for (int b = 0; b < B; ++b) max_blocks = std::max(max_blocks, active_[run[start + b]].table.len());
+      std::vector<uint32_t> tokens(B), chosen(B);
+      std::vector<int32_t> positions(B), lens(B), tables((size_t)B * max_blocks, -1);
+      for (int b = 0; b < B; ++b) {
+        const Sequence& s = active_[run[start + b]];
+        tokens[b] = s.token_ids.back();
+        positions[b] = (int32_t)(s.token_ids.size() - 1);
+        lens[b] = (int32_t)s.table.len();
+        for (size_t i = 0; i < s.table.len(); ++i) tables[(size_t)b * max_blocks + i] = s.table.slots()[i].block;
+      }
+      check(pi_model_decode_batch(ctx_, model_, pool_, tokens.data(), positions.data(), tables.data(), (int)max_blocks, lens.data(), B,
+                                  nullptr, chosen.data()),
+            "pi_model_decode_batch");
+      ++stats_.decode_batches;
+      for (int b = 0; b < B; ++b) {   // commit
+        Sequence& s = active_[run[start + b]];
+        s.token_ids.push_back(chosen[b]);
+        s.generated.push_back(chosen[b]);
+        ++stats_.generated_tokens;
+        if (chosen[b] == cfg_.eos_token) s.finished = FinishReason::Eos;
+        else if (s.generated.size() >= s.max_tokens) s.finished = FinishReason::Length;
+      }
     }
   }
 

@@ -24,6 +24,7 @@ PI_SPLIT_NONE, PI_SPLIT_COLUMN, PI_SPLIT_ROW = 0, 1, 2
 PI_F32, PI_INT8, PI_BF16 = 0, 1, 2
 PROF_CLASSES = ("gemv", "gemm_tc", "attention", "rope_kv", "other", "collective")
 PI_OPT_TENSOR_GEMM, PI_OPT_CUDA_GRAPH, PI_OPT_PDL, PI_OPT_GEMV_MAX_M, PI_OPT_ATTN_TMA, PI_OPT_FUSE_PLANES, PI_OPT_ATTN_SHARED = 1, 2, 3, 4, 5, 6, 7
+PI_OPT_PEER_SPIN_LIMIT = 8
 
 
 class PiError(RuntimeError):
@@ -71,6 +72,9 @@ SIGNATURES = {
     "pi_ctx_create_tp": (_I, [_I, _P, _I, _I, _P, _PP]),
     "pi_tp_peer_export": (_I, [_P, _SZ, _P]),
     "pi_tp_peer_import": (_I, [_P, _P]),
+    "pi_tp_peer_base": (_P, [_P]),
+    "pi_tp_peer_import_pointers": (_I, [_P, _PP]),
+    "pi_tp_exchange_add": (_I, [_P, _P, _P, _I, _I]),
     "pi_ctx_destroy": (None, [_P]),
     "pi_ctx_synchronize": (_I, [_P]),
     "pi_ctx_kernel_launches": (C.c_uint64, [_P]),
@@ -111,6 +115,8 @@ SIGNATURES = {
     "pi_model_create_synthetic": (_I, [_P, C.POINTER(ModelConfigC), C.c_uint64, C.c_float, _I, _I, _PP]),
     "pi_model_destroy": (None, [_P]),
     "pi_model_weight_bytes": (_SZ, [_P]),
+    "pi_model_max_batch": (_I, [_P]),
+    "pi_model_decode_batch_rows": (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _P, _P]),
     "pi_model_decode_batch": (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "pi_model_prefill": (_I, [_P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _P]),
     "pi_model_decode_multi": (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P]),

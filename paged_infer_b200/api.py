@@ -100,6 +100,21 @@ class Context:
             raise PiError(_lib.PI_ERR_INVALID_ARG, "one 64-byte handle per rank is needed")
         check(_lib.lib().pi_tp_peer_import(self.handle, C.create_string_buffer(raw, len(raw))), self.handle)
 
+    def tp_peer_base(self) -> int:
+        """Device address of this rank's exchange buffers (after :meth:`tp_peer_export`)."""
+        return int(_lib.lib().pi_tp_peer_base(self.handle) or 0)
+
+    def tp_peer_import_pointers(self, bases) -> None:
+        """Single-process set-up: ``bases`` = :meth:`tp_peer_base` of every rank's context, in rank order."""
+        if len(bases) != self.tp:
+            raise PiError(_lib.PI_ERR_INVALID_ARG, "one base pointer per rank is needed")
+        arr = (C.c_void_p * self.tp)(*[int(b) for b in bases])
+        check(_lib.lib().pi_tp_peer_import_pointers(self.handle, arr), self.handle)
+
+    def tp_exchange_add(self, partial_dev, x_dev, rows: int, cols: int) -> None:
+        """``x += sum over ranks of partial`` for [rows, cols] device matrices (``pi_tp_exchange_add``)."""
+        check(_lib.lib().pi_tp_exchange_add(self.handle, _dev_ptr(partial_dev), _dev_ptr(x_dev), rows, cols), self.handle)
+
 
 def nccl_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
@@ -593,6 +608,21 @@ class LlamaWeights:
         if want_logits and want_argmax:
             return logits, ids
         return logits if want_logits else ids
+
+    def decode_batch_rows(self, tokens, positions, block_tables, kv_cache: KvCache, logit_rows):
+        """One batched step that returns the greedy ids of all rows and the full logits of ``logit_rows`` only
+        (what Engine::run_groups reads per sequence, src/engine.rs:742-755): ``(logits [len(logit_rows), vocab], ids [B])``."""
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        positions = _i32(positions)
+        B = tokens.size
+        mat, lens, mb = pack_block_tables(block_tables)
+        rows = _i32(list(logit_rows))
+        logits = np.empty((rows.size, self.config.vocab_size), np.float32)
+        ids = np.empty(B, np.uint32)
+        check(_lib.lib().pi_model_decode_batch_rows(self.ctx.handle, self.handle, kv_cache.handle, _ptr(tokens), _ptr(positions),
+                                                    _ptr(mat), mb, _ptr(lens), B, _ptr(rows) if rows.size else None, int(rows.size),
+                                                    _ptr(logits) if rows.size else None, _ptr(ids)), self.ctx.handle)
+        return logits, ids
 
     def decode_multi(self, tokens, positions, block_tables, kv_cache: KvCache, n_steps: int) -> np.ndarray:
         """``n_steps`` greedy decode steps without host round trips; returns token ids [n_steps, B]."""

@@ -19,6 +19,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libpaged_infer_cuda.so")
+HOST_SRC = os.path.join(HERE, "host", "pi_host_shim.cpp")
+HOST_LIB = os.path.join(HERE, "libpaged_infer_host.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
@@ -77,7 +79,21 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("linking libpaged_infer_cuda.so failed")
+    build_host()
     return LIB
+
+
+def build_host() -> str:
+    """``libpaged_infer_host.so``: the C ABI over the host-side block bookkeeping (g++ only, no CUDA)."""
+    deps = [HOST_SRC, os.path.join(INCLUDE, "paged_infer_memory.hpp")]
+    if _newer(HOST_LIB, deps):
+        gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+        r = subprocess.run([gxx, "-std=c++17", "-O2", "-Wall", "-Wextra", "-fPIC", "-shared", HOST_SRC, "-o", HOST_LIB],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("building libpaged_infer_host.so failed")
+    return HOST_LIB
 
 
 if __name__ == "__main__":

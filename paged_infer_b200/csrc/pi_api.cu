@@ -75,6 +75,13 @@ static pi_status check_device_flag(pi_ctx* ctx) {
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (flag != 0) {
     PI_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    if (flag == 9) {
+      // a peer never delivered its partial sums: the slots of the ranks are out of step from here on, so the
+      // peer-memory exchange is retired and later steps go through NCCL (or fail loudly without a communicator)
+      ctx->peer.ready = false;
+      return pi_fail(ctx, PI_ERR_TIMEOUT, "a tensor-parallel peer did not deliver its partial sums in time (code 9); "
+                                          "the results of this step are invalid and the peer-memory exchange is disabled");
+    }
     return pi_fail(ctx, PI_ERR_TIMEOUT, "a kernel's bounded wait ran out (code %d)", flag);
   }
   return PI_OK;
@@ -133,11 +140,10 @@ pi_status pi_ctx_create(int device, void* stream, pi_ctx** out) { return ctx_cre
 pi_status pi_ctx_create_tp(int device, void* stream, int rank, int tp, const void* nccl_unique_id, pi_ctx** out) {
   if (!(tp == 1 || tp == 2 || tp == 4 || tp == 8) || rank < 0 || rank >= tp)
     return pi_fail(nullptr, PI_ERR_INVALID_ARG, "tensor-parallel rank %d of %d (tp must be 1, 2, 4 or 8)", rank, tp);
-  if (tp > 1 && !nccl_unique_id) return pi_fail(nullptr, PI_ERR_INVALID_ARG, "nccl_unique_id is NULL");
   PI_TRY(ctx_create_common(device, stream, out));
   (*out)->rank = rank;
   (*out)->tp = tp;
-  if (tp > 1) {
+  if (tp > 1 && nccl_unique_id) {
     pi_status s = pi_tp_init(*out, nccl_unique_id);
     if (s != PI_OK) {
       g_create_error = (*out)->err;
@@ -211,6 +217,10 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_ATTN_TMA: ctx->opt_attn_tma = value; return PI_OK;
     case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
+    case PI_OPT_PEER_SPIN_LIMIT:
+      PI_REQUIRE(ctx, value >= 0, "the spin limit cannot be negative");
+      ctx->peer_spin_limit = (uint32_t)value;
+      return PI_OK;
     case PI_OPT_GEMV_MAX_M:
       PI_REQUIRE(ctx, value >= 1, "gemv max M must be at least 1");
       ctx->opt_gemv_max_m = value;

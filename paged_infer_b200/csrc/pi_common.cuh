@@ -77,6 +77,7 @@ struct pi_ctx {
     void* mapped[8] = {};                       // what cudaIpcOpenMemHandle returned (to close)
     int next_slot = 0;
   } peer;
+  uint32_t peer_spin_limit = 0;   // polls a rank waits for a peer's partial sums; 0 = the default (about a second)
 
   // options
   bool opt_tensor_gemm = true;

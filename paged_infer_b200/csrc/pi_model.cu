@@ -633,6 +633,29 @@ void pi_model_destroy(pi_model* m) {
 }
 
 size_t pi_model_weight_bytes(const pi_model* m) { return m ? m->weight_bytes : 0; }
+int pi_model_max_batch(const pi_model* m) { return m ? m->capacity : 0; }
+
+pi_status pi_model_decode_batch_rows(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host,
+                                     const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,
+                                     const int32_t* table_lens_host, int B, const int32_t* logit_rows_host, int n_logit_rows,
+                                     float* logits_host, uint32_t* argmax_host) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, m && argmax_host, "null pointer");
+  PI_REQUIRE(ctx, n_logit_rows >= 0 && n_logit_rows <= B && (n_logit_rows == 0 || (logit_rows_host && logits_host)),
+             "%d rows of logits were asked for out of %d", n_logit_rows, B);
+  for (int i = 0; i < n_logit_rows; ++i)
+    PI_REQUIRE(ctx, logit_rows_host[i] >= 0 && logit_rows_host[i] < B, "logits of row %d of a batch of %d", logit_rows_host[i], B);
+  // the forward and the greedy ids; the ids' copy is queued, the selected rows follow on the same stream
+  PI_TRY(pi_model_decode_batch(ctx, m, pool, tokens_host, positions_host, block_tables_host, max_blocks, table_lens_host, B,
+                               nullptr, nullptr));
+  PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
+  PI_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax_dev, B * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  const size_t vocab = (size_t)m->cfg.vocab_size;
+  for (int i = 0; i < n_logit_rows; ++i)
+    PI_CUDA(ctx, cudaMemcpyAsync(logits_host + (size_t)i * vocab, m->logits + (size_t)logit_rows_host[i] * vocab,
+                                 vocab * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  return pi_ctx_synchronize(ctx);
+}
 
 pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host,
                                 const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,

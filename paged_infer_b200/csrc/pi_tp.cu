@@ -96,6 +96,7 @@ void pi_tp_destroy(pi_ctx* ctx) {
 
 pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n) {
   if (ctx->tp == 1 || n == 0) return PI_OK;
+  if (!ctx->nccl_comm) return pi_fail(ctx, PI_ERR_NCCL, "this tensor-parallel context has no NCCL communicator (created without a unique id) and its peer-memory exchange is not usable");
   pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
   PI_NCCL(ctx, nccl()->AllReduce(buf, buf, n, ncclFloat32, ncclSum, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->stream));
   return PI_OK;
@@ -106,6 +107,7 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
     PI_CUDA(ctx, cudaMemcpyAsync(recv, send, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
     return PI_OK;
   }
+  if (!ctx->nccl_comm) return pi_fail(ctx, PI_ERR_NCCL, "this tensor-parallel context has no NCCL communicator (created without a unique id)");
   PI_NCCL(ctx, nccl()->AllGather(send, recv, bytes_per_rank, ncclInt8, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->stream));
   return PI_OK;
 }
@@ -119,7 +121,6 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
 namespace {
 constexpr int kPeerSlots = 2;
 constexpr int kPeerMaxTp = 8;
-constexpr uint32_t kPeerSpinLimit = 1u << 22;
 
 struct PeerReduceParams {
   float* x;                          // [rows][cols] residual stream, updated in place
@@ -130,6 +131,7 @@ struct PeerReduceParams {
   unsigned long long* epoch;         // local: epoch[slot]
   unsigned int* ticket;              // local: ticket[slot]
   int* err_flag;
+  uint32_t spin_limit;               // polls (64 ns apart) before the wait for a peer gives up
   // optional: the new residual rows as bf16 planes (times a norm weight) + per-chunk sums of squares
   unsigned short* emit_base;
   size_t emit_plane_stride;
@@ -154,7 +156,10 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {   // never from a
 
 constexpr int kPeerChunk = 1024;     // floats of one row handled by one CTA pass (256 threads x float4)
 
-// grid <= number of SMs (all CTAs resident: they all read the epoch before the last one to finish advances it).
+// Every CTA reads the slot's epoch at its start and takes a ticket at its end; the CTA that draws the last ticket
+// advances the epoch, so no CTA of this launch can read the advanced value (the grid is kept <= the SM count only to
+// keep the waiting CTAs few).  A wait that runs out sets the context's error word and skips the add: the kernel
+// always returns.
 __global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduceParams p) {
   __shared__ int s_ok;
   __shared__ float s_red[8];
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduc
       const unsigned long long* f = p.flags[p.rank] + (size_t)p.slot * kPeerMaxTp + r;
       uint32_t spin = 0;
       while (ld_acquire_sys(f) < e) {
-        if (++spin >= kPeerSpinLimit) {
+        if (++spin >= p.spin_limit) {
           ok = 0;
           break;
         }
@@ -284,6 +289,38 @@ extern "C" pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles) {
   return PI_OK;
 }
 
+extern "C" void* pi_tp_peer_base(const pi_ctx* ctx) { return ctx ? ctx->peer.base : nullptr; }
+
+extern "C" pi_status pi_tp_peer_import_pointers(pi_ctx* ctx, void* const* bases) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, bases && ctx->peer.base, "call pi_tp_peer_export first");
+  PI_REQUIRE(ctx, bases[ctx->rank] == ctx->peer.base, "entry %d of the pointer table must be this context's own buffer", ctx->rank);
+  for (int r = 0; r < ctx->tp; ++r) {
+    PI_REQUIRE(ctx, bases[r] != nullptr, "rank %d has no buffer", r);
+    ctx->peer.data[r] = static_cast<float*>(bases[r]);
+    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(bases[r]) + peer_flags_offset(ctx->peer.slot_floats));
+  }
+  ctx->peer.next_slot = 0;
+  ctx->peer.ready = true;
+  return PI_OK;
+}
+
+extern "C" pi_status pi_tp_exchange_add(pi_ctx* ctx, const float* partial_dev, float* x_dev, int rows, int cols) {
+  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_REQUIRE(ctx, partial_dev && x_dev && rows > 0 && cols > 0, "null pointer or empty matrix");
+  const size_t n = (size_t)rows * cols;
+  if (ctx->tp == 1) return pi_launch_add(ctx, x_dev, partial_dev, n);
+  if (pi_tp_peer_usable(ctx, n) && cols % 4 == 0 && (uintptr_t)x_dev % 16 == 0) {
+    PI_CUDA(ctx, cudaMemcpyAsync(pi_tp_peer_slot(ctx), partial_dev, n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    return pi_tp_peer_reduce_add(ctx, x_dev, rows, cols);
+  }
+  PI_TRY(pi_reserve(ctx, &ctx->staging_in, n * sizeof(float)));
+  float* tmp = static_cast<float*>(ctx->staging_in.ptr);
+  PI_CUDA(ctx, cudaMemcpyAsync(tmp, partial_dev, n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+  PI_TRY(pi_tp_all_reduce_sum(ctx, tmp, n));
+  return pi_launch_add(ctx, x_dev, tmp, n);
+}
+
 bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n) {
   return ctx->tp > 1 && ctx->peer.ready && n <= ctx->peer.slot_floats && n % 4 == 0;
 }
@@ -312,6 +349,7 @@ pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_ac
   p.epoch = epoch + slot;
   p.ticket = reinterpret_cast<unsigned int*>(epoch + kPeerSlots) + slot;
   p.err_flag = ctx->dev_err;
+  p.spin_limit = ctx->peer_spin_limit ? ctx->peer_spin_limit : (1u << 22);
   const int cpr = (cols + kPeerChunk - 1) / kPeerChunk;
   if (emit) {
     PI_REQUIRE(ctx, emit->base && emit->K == cols && emit->plane_stride % 4 == 0 && (uintptr_t)emit->base % 8 == 0,

@@ -45,7 +45,7 @@ def test_lm_head_shape(ctx, oracle):
     rows, cols = 32000, 2048
     q, s = oracle.quantize_rows_i8(normal_f32((rows, cols), 5, 0.02), rows, cols)
     p = api.Projection.int8(ctx, q, s)
-    for M in (1, 8, 64):
+    for M in (1, 8, 64, 128, 512):
         x = normal_f32((M, cols), 200 + M, 1.0)
         assert rel_err(p.apply_batched(x), oracle.matmat_i8(x, q, s)) < 2e-5, M
 

@@ -276,6 +276,30 @@ def test_batch_64_ragged_decode_with_shared_prefix_blocks(ctx, oracle):
     assert worst < 1e-3 and mism == 0, (worst, mism)
 
 
+def test_logits_of_selected_rows_only(ctx, oracle):
+    """The per-sequence hand-off of Engine::run_groups (src/engine.rs:742-755): ids for everyone, full logits only for
+    the rows the host samples itself."""
+    from paged_infer_b200 import api
+    cfg, om, gm = small_llama(ctx, oracle, 6)
+    rng = np.random.default_rng(6)
+    B = 9
+    lens = [int(x) for x in rng.integers(3, 40, B)]
+    tables = [[b * 4 + i for i in range(4)] for b in range(B)]
+    kv = api.KvCache(ctx, gm.kv_layout(4 * B, BLOCK))
+    kv.upload(np.zeros(kv_floats(cfg, 4 * B), np.float32))
+    for b in range(B):
+        gm.prefill_batched(rng.integers(0, cfg.vocab_size, lens[b]).astype(np.uint32), 0, tables[b], kv, 16)
+    tok = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
+    full, ids = gm.decode_batch_into(tok, lens, tables, kv, want_argmax=True)
+    some, ids2 = gm.decode_batch_rows(tok, lens, tables, kv, [7, 0, 3])      # same step again: same KV values rewritten
+    assert ids2.tolist() == ids.tolist()
+    assert np.array_equal(some, full[[7, 0, 3]])
+    none, ids3 = gm.decode_batch_rows(tok, lens, tables, kv, [])
+    assert none.shape == (0, cfg.vocab_size) and ids3.tolist() == ids.tolist()
+    with pytest.raises(api.PiError, match="row 9"):
+        gm.decode_batch_rows(tok, lens, tables, kv, [9])
+
+
 def test_multi_step_decode_equals_step_by_step(ctx, oracle):
     """n greedy steps in one call (eager first step, then a replayed CUDA graph) == n single-step calls."""
     from paged_infer_b200 import api

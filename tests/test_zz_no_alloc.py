@@ -10,7 +10,11 @@ out of a fixed ~3 MiB area that is part of the library image instead.
 The test calls it through the C ABI twice in a row - the second call on a
 different matrix with fewer activation rows, so anything stale in the shared
 scratch area would show - and compares each result with the ordinary entry
-point's (same kernels, so the 2e-5 tolerance of the tensor-GEMM tests is generous).
+point's (same kernels, so the 2e-5 tolerance of the tensor-GEMM tests is generous)
+and with the CPU oracle's int8 matmat, so a defect shared by both entry points
+would show as well.  Two more cases cover what the entry point exists for: the
+very first projection of a fresh context goes through it (its own set-up path),
+and a warmed call leaves the amount of free device memory unchanged.
 It lives in its own file, collected last, so that a run that stops at the first
 failure has already run every other test.
 """
@@ -26,7 +30,7 @@ def _device_buffers(torch, M, K, N, seed):
     return x, torch.full((M, N), float("nan"), device="cuda"), torch.full((M, N), float("nan"), device="cuda")
 
 
-def test_noalloc_projection_matches_the_ordinary_one_twice_in_a_row():
+def test_noalloc_projection_matches_the_ordinary_one_twice_in_a_row(oracle):
     import torch
 
     from paged_infer_b200 import api
@@ -34,11 +38,12 @@ def test_noalloc_projection_matches_the_ordinary_one_twice_in_a_row():
     ctx = api.Context(0)
     rng = np.random.default_rng(11)
     cases = [(64, 2048, 2560), (17, 5632, 2048)]   # (activation rows, columns, rows): second call is smaller in M
-    lins = []
+    lins, codes = [], []
     for M, K, N in cases:
         q = rng.integers(-127, 128, (N, K), dtype=np.int8)
         s = (rng.random(N, dtype=np.float32) + 0.5) * 1e-3
         lins.append(api.Projection.int8(ctx, q, s))
+        codes.append((q, s))
     for call, ((M, K, N), lin) in enumerate(zip(cases, lins)):
         x, want, got = _device_buffers(torch, M, K, N, 100 + call)
         torch.cuda.synchronize()
@@ -49,6 +54,8 @@ def test_noalloc_projection_matches_the_ordinary_one_twice_in_a_row():
         assert np.isfinite(g).all(), f"call {call}: output not fully written"
         scale = np.maximum(np.abs(w), 1.0)
         assert (np.abs(g - w) / scale).max() < 2e-5, f"call {call}"
+        ref = oracle.matmat_i8(x.cpu().numpy(), *codes[call])
+        assert (np.abs(g - ref) / np.maximum(np.abs(ref), 1.0)).max() < 2e-5 * max(1.0, (K / 2048.0) ** 0.5), f"call {call} vs the CPU oracle"
     # and once more on the first matrix: the area still holds the second call's planes
     M, K, N = cases[0]
     x, want, got = _device_buffers(torch, M, K, N, 7)
@@ -57,6 +64,41 @@ def test_noalloc_projection_matches_the_ordinary_one_twice_in_a_row():
     lins[0].apply_device_noalloc(x, got, M)
     ctx.synchronize()
     assert (np.abs(got.cpu().numpy() - want.cpu().numpy()) / np.maximum(np.abs(want.cpu().numpy()), 1.0)).max() < 2e-5
+    ctx.close()
+
+
+def test_noalloc_first_call_on_a_fresh_context_small_batch_and_no_allocation(oracle):
+    """The first projection a new context ever runs goes through the allocation-free entry point (so its own set-up,
+    not the ordinary call's, prepares the kernels), with 3 activation rows - fewer than the ordinary call would send
+    to the tensor path; then a warmed call must leave the free device memory exactly where it was."""
+    import torch
+
+    from paged_infer_b200 import api
+
+    torch.cuda.init()
+    torch.zeros(1, device="cuda")
+    ctx = api.Context(0)
+    rng = np.random.default_rng(5)
+    M, K, N = 3, 1024, 384
+    q = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    s = (rng.random(N, dtype=np.float32) + 0.5) * 1e-3
+    lin = api.Projection.int8(ctx, q, s)
+    x, _, got = _device_buffers(torch, M, K, N, 1)
+    torch.cuda.synchronize()
+    lin.apply_device_noalloc(x, got, M)          # first projection of this context
+    ctx.synchronize()
+    ref = oracle.matmat_i8(x.cpu().numpy(), q, s)
+    assert (np.abs(got.cpu().numpy() - ref) / np.maximum(np.abs(ref), 1.0)).max() < 2e-5
+    x2, _, got2 = _device_buffers(torch, 64, K, N, 2)
+    torch.cuda.synchronize()
+    lin.apply_device_noalloc(x2, got2, 64)       # warm the widest tile as well
+    ctx.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        lin.apply_device_noalloc(x2, got2, 64)
+        lin.apply_device_noalloc(x, got, M)
+    ctx.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
     ctx.close()
 
 
