@@ -1,0 +1,601 @@
+// A chain of dequant projections in ONE persistent launch (batches of up to 64 activation rows).
+//
+// A decode step is a chain of dependent projections with nothing between them but their own epilogues:
+// o -> [gate;up] -> down -> next layer's [q;k;v] (-> LM head after the last layer).  Launched one by one, each pays a
+// launch hop, a prologue (TMEM allocation, barriers, first weight loads), idle SMs when its row tiles do not fill
+// the machine, and a tear-down.  Here up to four consecutive projections ("phases") run in one grid of one CTA per
+// SM that stays resident for all of them:
+//
+//   * every phase's work is its (row tile, K block) units in row-tile-major order, cut into equal contiguous shares,
+//     one per CTA - a wide matrix ([gate;up]: 88 row tiles) and a narrow one (o, down: 16) both keep all SMs busy;
+//   * a CTA's share is a few "segments" (a K range of one row tile).  A segment that covers a tile's whole K range
+//     goes straight to the epilogue; otherwise the raw partial tile goes to a scratch slot in global memory and
+//     the CTA that hands in the LAST partial of the tile adds all of them IN SLOT ORDER and runs the epilogue, so
+//     the result does not depend on timing and nobody ever waits for a peer;
+//   * between phases a grid-wide barrier (sense reversing, in global memory); a CTA's weight producers do not wait
+//     for it - the next phase's weights are already on their way into registers and tensor memory while the barrier
+//     is pending; only the activation loads (TMA) of the next phase do;
+//   * TMEM, the mbarriers and the pipeline state are set up once.
+//
+// The inner machinery is that of the single-projection kernel (pi_gemm_tc.cu): swap-AB tcgen05.mma kind::f16 with
+// the widened int8 weights as the A operand in tensor memory, the activations as three exact bf16 planes fetched by
+// one 3-D TMA box per K atom, f32 accumulation in tensor memory, and the same epilogues (pi_gemm_tc.cuh).  Every
+// wait is bounded; a wait that runs out raises the context's error word and the kernel winds down.
+//
+// Replaces math::matmat_i8_weight_parallel + transpose_rb_to_br (reference src/math.rs:223-290) for the batched
+// decode step, with math::rms_norm (src/math.rs:4-22), the rotary embedding and KV write (src/model.rs:1065-1107),
+// SwiGLU and the residual adds (src/model.rs:1127-1167) folded into the epilogues.
+#include <algorithm>
+#include <new>
+
+#include "pi_gemm_tc.cuh"
+
+namespace {
+using namespace pi_tc;
+
+constexpr int kMaxPhases = 4;
+constexpr uint32_t kGridSpinLimit = 1u << 22;   // polls, 32 ns apart
+
+struct ChainParams {
+  GemmParams ph[kMaxPhases];
+  int rtiles[kMaxPhases];
+  int active[kMaxPhases];     // CTAs that own units of the phase: min(grid, units)
+  int nphases;
+  float* partials;            // [slots][BN][128] raw partial tiles
+  unsigned int* tickets;      // [row tiles] partials handed in; zero between uses
+  unsigned int* bar_count;    // grid barrier: arrivals of the pending generation
+  unsigned int* bar_gen;      // generations completed since the buffer was cleared
+  int* err_flag;
+};
+struct ChainMaps {
+  CUtensorMap m[kMaxPhases];
+};
+
+// This CTA's units, phase after phase.
+struct UnitIter {
+  int ph;      // phase of the current unit; nphases at the end
+  int tile, kb;
+  int left;    // units left in this CTA's share of the phase, the current one included
+  int nkb;
+  bool first;  // the current unit opens a segment
+};
+
+__device__ __forceinline__ void iter_enter(UnitIter& it, const ChainParams& cp, int cta) {
+  while (it.ph < cp.nphases) {
+    const int nkb = cp.ph[it.ph].nkb, act = cp.active[it.ph];
+    if (cta < act) {
+      const long U = (long)cp.rtiles[it.ph] * nkb;
+      const long u0 = U * cta / act, u1 = U * (cta + 1) / act;
+      it.nkb = nkb;
+      it.tile = (int)(u0 / nkb);
+      it.kb = (int)(u0 - (long)it.tile * nkb);
+      it.left = (int)(u1 - u0);
+      it.first = true;
+      return;
+    }
+    ++it.ph;
+  }
+}
+__device__ __forceinline__ bool iter_seg_last(const UnitIter& it) { return it.left == 1 || it.kb == it.nkb - 1; }
+__device__ __forceinline__ void iter_next(UnitIter& it, const ChainParams& cp, int cta) {
+  it.first = iter_seg_last(it);
+  --it.left;
+  ++it.kb;
+  if (it.left == 0) {
+    ++it.ph;
+    iter_enter(it, cp, cta);
+    return;
+  }
+  if (it.kb == it.nkb) {
+    it.kb = 0;
+    ++it.tile;
+  }
+}
+// The CTA whose share holds unit x of a phase with U units cut into `act` shares (share c = [U*c/act, U*(c+1)/act)).
+__device__ __forceinline__ int owner_of(long x, long U, int act) { return (int)(((x + 1) * act - 1) / U); }
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait on an mbarrier; polls are only counted once the grid dependency of this launch is resolved (until
+// then nothing can make progress and the wait is the preceding kernel's, however long that runs).
+__device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, const volatile int* dep_ok) {
+  for (uint32_t spin = 0; spin < kSpinLimit;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*dep_ok) ++spin;
+  }
+  return false;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant__ ChainMaps maps) {
+  constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
+  constexpr int kBStageBytes = 2 * kBAtomBytes;
+  constexpr int kDCols = kPlanes * BN;
+  constexpr int kAStart = (kDCols + 63) / 64 * 64;          // weight stages start on a 64-column boundary
+  static_assert(kDCols <= 256, "one MMA covers at most 256 accumulator columns");
+  static_assert(kAStart + STAGES * kACols <= 512, "TMEM holds 512 columns");
+  constexpr int kTmemCols = 512;
+  constexpr int kEpiWarps = BN >= 32 ? kParkWarps : 4;      // warps that move the accumulator out of TMEM
+  constexpr int kTileFloats = BN * kBM;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 2];
+  __shared__ uint32_t s_tmem;
+  __shared__ unsigned int s_base_gen;
+  __shared__ volatile int s_abort;
+  __shared__ volatile int s_dep_ok;
+  __shared__ int s_last;           // this CTA handed in the last partial of the tile
+  __shared__ float s_rowf[BN];     // row factor of the activation rows
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3, kq = (warp >> 2) & 3, half = (warp >> 2) & 1;
+  const int cta = blockIdx.x, G = gridDim.x;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const uint32_t accum_full = smem_u32(&bars[2 * STAGES]), accum_empty = smem_u32(&bars[2 * STAGES + 1]);
+  float* my_part = reinterpret_cast<float*>(smem + STAGES * kBStageBytes);   // [BN][128], apart from the B stages
+  pi_grid_launch_dependents();
+
+  // ---- weight producers: the first group of loads goes out before anything else (weights depend on nothing) ----
+  constexpr int kGroup = 4;
+  uint32_t cur[kGroup][8], nxt[kGroup][8];
+  UnitIter pf;   // prefetch position, up to two groups ahead of the unit being widened
+  pf.ph = 0;
+  auto unit_ptr = [&](const UnitIter& u) {
+    const GemmParams& p = cp.ph[u.ph];
+    const int row = min(u.tile * kBM + quad * 32 + lane, p.N - 1);
+    return reinterpret_cast<const unsigned char*>(p.W) + (size_t)row * p.ld + (size_t)u.kb * kBK + kq * 32;
+  };
+  if (warp < kProducerWarps) {
+    iter_enter(pf, cp, cta);
+#pragma unroll
+    for (int d = 0; d < kGroup; ++d)
+      if (pf.ph < cp.nphases) {
+        ld_stream_32(unit_ptr(pf), &cur[d][0]);
+        iter_next(pf, cp, cta);
+      }
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, kProducerWarps + 1);       // one arrival per producer warp + the TMA thread's expect_tx
+      mbar_init(empty0 + 8 * s, 1);                        // one tcgen05.commit
+    }
+    mbar_init(accum_full, 1);
+    mbar_init(accum_empty, kEpiWarps);
+    s_abort = 0;
+    s_dep_ok = 0;
+    s_base_gen = ld_acquire_u32(cp.bar_gen);   // cannot move before this CTA's own first arrival
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == kProducerWarps + 1) {  // TMEM allocation is warp-wide
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  const uint32_t tmem_a0 = tmem + (uint32_t)kAStart;
+  const uint32_t smem_base = smem_u32(smem);
+  const unsigned int base_gen = s_base_gen;
+
+  // Wait until `need` grid barriers of this launch have completed; false when the limit ran out.
+  auto grid_wait = [&](int need) {
+    for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+      if ((int)(ld_acquire_u32(cp.bar_gen) - base_gen) >= need) return true;
+      if (s_abort) return false;
+      __nanosleep(32);
+    }
+    return false;
+  };
+
+  if (warp < kProducerWarps) {
+    // ================= weight producers + epilogue =================================================================
+    UnitIter cu;
+    cu.ph = 0;
+    iter_enter(cu, cp, cta);
+    bool dep_waited = false;
+    int it = 0, sg = 0, seg_kb0 = 0;
+    int arrived = 0;   // grid barriers this CTA has arrived at (thread 0 only)
+    // Arrive at the barriers that end phases [arrived, upto): thread 0, after every thread's stores of the phase.
+    auto arrive_upto = [&](int upto) {
+      upto = min(upto, cp.nphases - 1);   // nothing follows the last phase
+      for (; arrived < upto; ++arrived) {
+        if (arrived > 0 && !grid_wait(arrived)) {   // the previous generation must be over before this arrival counts
+          if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
+          s_abort = 1;
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
+        __threadfence();
+        const unsigned int old = atomicAdd(cp.bar_count, 1u);
+        if (old == (unsigned int)G - 1u) {
+          *reinterpret_cast<volatile unsigned int*>(cp.bar_count) = 0u;
+          __threadfence();
+          atomicAdd(cp.bar_gen, 1u);
+        }
+      }
+    };
+    if (tid == 0) arrive_upto(cu.ph);   // phases in which this CTA has nothing to do
+
+    const uint32_t my_a = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(kq * 16);
+    const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
+    // Once a wait has run out (s_abort) the warps stop waiting and stop feeding the pipeline, but they still walk
+    // their units to the end: the named barriers of the epilogues below must be reached by all 16 warps in lock step.
+    while (cu.ph < cp.nphases) {
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d)
+        if (pf.ph < cp.nphases) {
+          ld_stream_32(unit_ptr(pf), &nxt[d][0]);
+          iter_next(pf, cp, cta);
+        }
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d) {
+        if (cu.ph >= cp.nphases) break;
+        const int s = it % STAGES;
+        if (cu.first) seg_kb0 = cu.kb;
+        uint32_t h[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
+        int ok = 1;
+        if (lane == 0) ok = (!s_abort && mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");   // the MMAs that read this stage are done
+          tmem_st16(my_a + (uint32_t)(s * kACols), h);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full0 + 8 * s);
+        } else if (lane == 0 && !s_abort) {
+          s_abort = 1;
+          if (cp.err_flag) atomicExch(cp.err_flag, 2);
+        }
+        ++it;
+
+        if (iter_seg_last(cu)) {
+          // ---- the segment [seg_kb0, cu.kb] of row tile cu.tile is in flight: take its accumulator and finish it ----
+          const int ph = cu.ph, tile = cu.tile;
+          const GemmParams& p = cp.ph[ph];
+          const bool whole = seg_kb0 == 0 && cu.kb == p.nkb - 1;
+          const long U = (long)cp.rtiles[ph] * p.nkb;
+          const int act = cp.active[ph];
+          const int c_first = owner_of((long)tile * p.nkb, U, act), c_last = owner_of((long)(tile + 1) * p.nkb - 1, U, act);
+          if (!dep_waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // the epilogue reads what the preceding kernel wrote
+            dep_waited = true;
+          }
+          float* part_dst = whole ? my_part : cp.partials + (size_t)(cta + tile) * kTileFloats;
+          if (warp < kParkWarps) {
+            int got = 0;
+            if (lane == 0) {
+              got = (!s_abort && mbar_wait_dep(accum_full, (uint32_t)(sg & 1), &s_dep_ok)) ? 1 : 0;
+              if (!got && !s_abort) {
+                s_abort = 1;
+                if (cp.err_flag) atomicExch(cp.err_flag, 5);
+              }
+            }
+            got = __shfl_sync(0xffffffffu, got, 0);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
+            if (BN >= 32 || half == 0) {
+#pragma unroll 1
+              for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+                float v[16];
+                if (got) {
+                  tmem_ld_sum16<BN>(my_d, c0, v);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) part_dst[(c0 + j) * kBM + quad * 32 + lane] = v[j];
+              }
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) mbar_arrive(accum_empty);   // the next segment's MMAs may overwrite the accumulator
+            }
+            if (!whole) __threadfence();
+          }
+          if (tid < BN) s_rowf[tid] = act_row_factor(p, tid);
+          EpiRows rows;
+          epi_rows_load(p, tile * kBM, tid, rows);
+          asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+          bool finish = true;
+          if (!whole) {   // hand the partial in; whoever hands in the last one of the tile finishes it
+            if (tid == 0) {
+              const unsigned int n = (unsigned int)(c_last - c_first + 1);
+              const unsigned int t = atomicAdd(cp.tickets + tile, 1u);
+              s_last = (t == n - 1u) ? 1 : 0;
+              if (t == n - 1u) cp.tickets[tile] = 0u;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+            finish = s_last != 0;
+            if (finish) __threadfence();
+          }
+          if (finish) {
+            const int r4 = lane * 4, csub = warp;   // 16 activation rows in flight per pass
+            const int nparts = c_last - c_first + 1;
+            const float* slot0 = cp.partials + (size_t)(c_first + tile) * kTileFloats + r4;
+            for (int c = csub; c < BN; c += kProducerWarps) {
+              float4 acc;
+              if (whole) {
+                acc = *reinterpret_cast<const float4*>(my_part + c * kBM + r4);
+              } else {
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int j = 0; j < nparts; ++j) {   // slot order = K order: the same sum whoever adds it up
+                  const float4 v = __ldcg(reinterpret_cast<const float4*>(slot0 + (size_t)j * kTileFloats + c * kBM));
+                  acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+              }
+              epi_row(p, rows, tile, c, s_rowf[c], acc, lane);
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // stores issued, my_part and s_rowf free
+          ++sg;
+          if (cu.left == 1 && tid == 0) {   // that was this CTA's last segment of the phase
+            UnitIter nx = cu;
+            iter_next(nx, cp, cta);
+            arrive_upto(nx.ph);
+          }
+        }
+        iter_next(cu, cp, cta);
+      }
+#pragma unroll
+      for (int d = 0; d < kGroup; ++d)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[d][i] = nxt[d][i];
+    }
+    if (tid == 0) arrive_upto(cp.nphases);   // after an abort: keep the barrier consistent for the other CTAs
+  } else if (warp == kProducerWarps) {
+    // ================= activation loader: one 3-D TMA box {64 K, BN rows, 3 planes} per K atom =====================
+    if (lane == 0) {
+      UnitIter cu;
+      cu.ph = 0;
+      iter_enter(cu, cp, cta);
+      int it = 0, ready_ph = -1;
+      bool issued = false;
+      asm volatile("griddepcontrol.wait;" ::: "memory");   // the first phase's planes come from the preceding kernel
+      s_dep_ok = 1;
+      while (cu.ph < cp.nphases) {
+        if (cu.ph != ready_ph) {
+          if (cu.ph > 0) {
+            if (!grid_wait(cu.ph)) {   // every CTA has finished the phases before this one
+              if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
+              s_abort = 1;
+              break;
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+          ready_ph = cu.ph;
+        }
+        const int s = it % STAGES;
+        if (s_abort) break;
+        if (!mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) {
+          s_abort = 1;
+          if (cp.err_flag) atomicExch(cp.err_flag, 3);
+          break;
+        }
+        const uint32_t bar = full0 + 8 * s;
+        const uint32_t b_stage = smem_base + s * kBStageBytes;
+        mbar_arrive_expect_tx(bar, kBStageBytes);
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+                  b_stage + atom * kBAtomBytes),
+              "l"(&maps.m[cu.ph]), "r"(bar), "r"(cu.kb * kBK + atom * 64), "r"(0), "r"(0)
+              : "memory");
+        }
+        issued = true;
+        ++it;
+        iter_next(cu, cp, cta);
+      }
+      if (s_abort && issued)   // copies may still be landing in this CTA's shared memory: give them time before it exits
+        for (int i = 0; i < 400; ++i) __nanosleep(100);
+    }
+  } else {
+    // ================= MMA issuer ==================================================================================
+    if (lane == 0) {
+      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = bf16, N = 3*BN, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kDCols >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      UnitIter cu;
+      cu.ph = 0;
+      iter_enter(cu, cp, cta);
+      int it = 0, sg = 0;
+      while (cu.ph < cp.nphases) {
+        const int s = it % STAGES;
+        if (cu.first && sg > 0) {   // the epilogue of the previous segment has emptied the accumulator
+          if (s_abort || !mbar_wait_dep(accum_empty, (uint32_t)((sg - 1) & 1), &s_dep_ok)) {
+            if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 7);
+            s_abort = 1;
+            break;
+          }
+        }
+        if (s_abort || !mbar_wait_dep(full0 + 8 * s, (it / STAGES) & 1, &s_dep_ok)) {
+          if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 4);
+          s_abort = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t db0 = smem_desc(smem_base + s * kBStageBytes);
+        const uint32_t a_s = tmem_a0 + (uint32_t)(s * kACols);
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {  // 16 K elements: 8 TMEM columns of A, 32 bytes of every B row
+            const uint64_t db = db0 + (uint64_t)((atom * kBAtomBytes + ks * 32) >> 4);
+            umma_f16_ts(tmem, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (!cu.first || atom + ks > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty0 + 8 * s);  // the stage (TMEM columns and shared tile) is free once these MMAs are done
+        if (iter_seg_last(cu)) {
+          umma_commit(accum_full);
+          ++sg;
+        }
+        ++it;
+        iter_next(cu, cp, cta);
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kProducerWarps + 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
+// ---- host side: the queue of a context ------------------------------------------------------------------------------
+struct ChainQueue {
+  ChainParams cp = {};
+  ChainMaps maps = {};
+  int n = 0, BN = 0;
+  bool open = false;
+  // scratch (global memory beyond the inputs and outputs): partial tiles, tickets, the grid barrier
+  void* ws = nullptr;
+  size_t ws_slots = 0, ws_tiles = 0;
+  int ws_bn = 0;
+};
+
+ChainQueue* queue_of(pi_ctx* ctx) {
+  if (!ctx->gemm_chain) ctx->gemm_chain = new (std::nothrow) ChainQueue();
+  return static_cast<ChainQueue*>(ctx->gemm_chain);
+}
+
+template <int BN, int STAGES>
+cudaError_t launch_chain(pi_ctx* ctx, const ChainQueue& q, int grid) {
+  constexpr size_t smem = (size_t)STAGES * (2 * kPlanes * BN * 128) + (size_t)BN * kBM * sizeof(float) + 1024;
+  auto k = gemm_chain_kernel<BN, STAGES>;
+  static pi_smem_grant granted;  // per instantiation
+  if (smem > granted.of(ctx)) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted.of(ctx) = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, k, q.cp, q.maps);
+}
+
+}  // namespace
+
+bool pi_gemm_chain_usable(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
+  return ctx->opt_gemm_chain && a.M <= 64 && pi_gemm_tc_supported(ctx, lin, a);
+}
+
+void pi_gemm_chain_open(pi_ctx* ctx) {
+  ChainQueue* q = queue_of(ctx);
+  if (q) q->open = true;
+}
+
+pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
+  ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
+  if (!q || q->n == 0) return PI_OK;
+  pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
+  const int BN = q->BN;
+  // one CTA per SM; every phase cuts its units into min(grid, units) shares
+  int grid = 1;
+  size_t slots = 0, tiles = 0;
+  for (int i = 0; i < q->n; ++i) {
+    const long U = (long)q->cp.rtiles[i] * q->cp.ph[i].nkb;
+    grid = std::max(grid, (int)std::min<long>(U, ctx->sm_count));
+  }
+  for (int i = 0; i < q->n; ++i) {
+    const long U = (long)q->cp.rtiles[i] * q->cp.ph[i].nkb;
+    q->cp.active[i] = (int)std::min<long>(U, grid);
+    slots = std::max(slots, (size_t)q->cp.active[i] + (size_t)q->cp.rtiles[i]);
+    tiles = std::max(tiles, (size_t)q->cp.rtiles[i]);
+  }
+  q->cp.nphases = q->n;
+  q->cp.err_flag = ctx->dev_err;
+  const int n = q->n;
+  q->n = 0;   // whatever happens below, the queue is empty afterwards
+  if (slots > q->ws_slots || tiles > q->ws_tiles || BN > q->ws_bn) {
+    // the buffer may still be in use by a queued launch
+    PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (q->ws) PI_CUDA(ctx, cudaFree(q->ws));
+    q->ws = nullptr;
+    q->ws_slots = std::max(slots, q->ws_slots);
+    q->ws_tiles = std::max(tiles, q->ws_tiles);
+    q->ws_bn = std::max(BN, q->ws_bn);
+    const size_t bytes = q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float) + (q->ws_tiles + 64) * sizeof(unsigned int);
+    PI_CUDA(ctx, cudaMalloc(&q->ws, bytes));
+    PI_CUDA(ctx, cudaMemsetAsync(q->ws, 0, bytes, ctx->stream));
+  }
+  q->cp.partials = static_cast<float*>(q->ws);
+  unsigned int* words = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(q->ws) + q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float));
+  q->cp.bar_count = words;          // a 128-byte line of its own
+  q->cp.bar_gen = words + 32;
+  q->cp.tickets = words + 64;
+  cudaError_t err;
+  switch (BN) {
+    case 16: err = launch_chain<16, 6>(ctx, *q, grid); break;
+    case 32: err = launch_chain<32, 6>(ctx, *q, grid); break;
+    default: err = launch_chain<64, 4>(ctx, *q, grid); break;
+  }
+  if (err != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "projection chain launch (%d phases) failed: %s", n, cudaGetErrorString(err));
+  ctx->launches++;
+  return PI_OK;
+}
+
+pi_status pi_gemm_chain_close(pi_ctx* ctx) {
+  ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
+  if (q) q->open = false;
+  return pi_gemm_chain_flush(ctx);
+}
+
+// After a bounded wait ran out the barrier words and tickets may be left mid-count: clear them (stream ordered).
+void pi_gemm_chain_reset_sync(pi_ctx* ctx) {
+  ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
+  if (!q || !q->ws) return;
+  unsigned char* words = static_cast<unsigned char*>(q->ws) + q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float);
+  cudaMemsetAsync(words, 0, (q->ws_tiles + 64) * sizeof(unsigned int), ctx->stream);
+}
+
+void pi_gemm_chain_destroy(pi_ctx* ctx) {
+  ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
+  if (!q) return;
+  if (q->ws) cudaFree(q->ws);
+  delete q;
+  ctx->gemm_chain = nullptr;
+}
+
+pi_status pi_gemm_chain_enqueue(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_act_planes& in) {
+  ChainQueue* q = queue_of(ctx);
+  if (!q) return pi_fail(ctx, PI_ERR_OOM, "host allocation failed");
+  const int BN = pi_tc::pick_bn(a.M);
+  if (q->n > 0 && (q->n == kMaxPhases || q->BN != BN || q->cp.ph[0].M != a.M)) PI_TRY(pi_gemm_chain_flush(ctx));
+  GemmParams p;
+  CUtensorMap map;
+  PI_TRY(pi_tc::build_gemm_params(ctx, lin, a, in, BN, &p, &map));
+  p.ksplit = 1;
+  q->cp.ph[q->n] = p;
+  q->maps.m[q->n] = map;
+  q->cp.rtiles[q->n] = (p.N + kBM - 1) / kBM;
+  q->BN = BN;
+  ++q->n;
+  if (!q->open) return pi_gemm_chain_flush(ctx);
+  return PI_OK;
+}
