@@ -100,6 +100,12 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
   return v;
 }
 
+__device__ __forceinline__ unsigned int atom_add_acq_rel(unsigned int* p, unsigned int v) {
+  unsigned int old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 // Bounded wait on an mbarrier; polls are only counted once the grid dependency of this launch is resolved (until
 // then nothing can make progress and the wait is the preceding kernel's, however long that runs).
 __device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, const volatile int* dep_ok) {
@@ -117,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, con
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(112)
 gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant__ ChainMaps maps) {
   constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
   constexpr int kBStageBytes = 2 * kBAtomBytes;
@@ -132,9 +138,9 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long bars[2 * STAGES + 2];
   __shared__ uint32_t s_tmem;
-  __shared__ unsigned int s_base_gen;
+  __shared__ volatile unsigned int s_base_gen;   // barrier generations completed before this launch began
   __shared__ volatile int s_abort;
-  __shared__ volatile int s_dep_ok;
+  __shared__ volatile int s_dep_ok;   // the preceding kernel has completed and s_base_gen is recorded
   __shared__ int s_last;           // this CTA handed in the last partial of the tile
   __shared__ float s_rowf[BN];     // row factor of the activation rows
 
@@ -175,7 +181,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
     mbar_init(accum_empty, kEpiWarps);
     s_abort = 0;
     s_dep_ok = 0;
-    s_base_gen = ld_acquire_u32(cp.bar_gen);   // cannot move before this CTA's own first arrival
+    s_base_gen = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -189,12 +195,15 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   const uint32_t tmem = s_tmem;
   const uint32_t tmem_a0 = tmem + (uint32_t)kAStart;
   const uint32_t smem_base = smem_u32(smem);
-  const unsigned int base_gen = s_base_gen;
 
+  // The barrier words are shared with the preceding launch, which may still be running while this one starts
+  // (programmatic dependent launch).  So the generation count "before this launch" is read only once the preceding
+  // kernel has completed (by the TMA lane, which then raises s_dep_ok), and no thread arrives at a barrier before
+  // that: no barrier of this launch can complete before every CTA has recorded the same base.
   // Wait until `need` grid barriers of this launch have completed; false when the limit ran out.
   auto grid_wait = [&](int need) {
     for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
-      if ((int)(ld_acquire_u32(cp.bar_gen) - base_gen) >= need) return true;
+      if (s_dep_ok && (int)(ld_acquire_u32(cp.bar_gen) - s_base_gen) >= need) return true;
       if (s_abort) return false;
       __nanosleep(32);
     }
@@ -213,17 +222,17 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
     auto arrive_upto = [&](int upto) {
       upto = min(upto, cp.nphases - 1);   // nothing follows the last phase
       for (; arrived < upto; ++arrived) {
-        if (arrived > 0 && !grid_wait(arrived)) {   // the previous generation must be over before this arrival counts
+        if (!grid_wait(arrived)) {   // the base is recorded and the previous generation is over before this arrival counts
           if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
           s_abort = 1;
         }
         asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
         __threadfence();
-        const unsigned int old = atomicAdd(cp.bar_count, 1u);
+        const unsigned int old = atom_add_acq_rel(cp.bar_count, 1u);
         if (old == (unsigned int)G - 1u) {
           *reinterpret_cast<volatile unsigned int*>(cp.bar_count) = 0u;
           __threadfence();
-          atomicAdd(cp.bar_gen, 1u);
+          atom_add_acq_rel(cp.bar_gen, 1u);
         }
       }
     };
@@ -316,7 +325,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
           if (!whole) {   // hand the partial in; whoever hands in the last one of the tile finishes it
             if (tid == 0) {
               const unsigned int n = (unsigned int)(c_last - c_first + 1);
-              const unsigned int t = atomicAdd(cp.tickets + tile, 1u);
+              const unsigned int t = atom_add_acq_rel(cp.tickets + tile, 1u);
               s_last = (t == n - 1u) ? 1 : 0;
               if (t == n - 1u) cp.tickets[tile] = 0u;
             }
@@ -343,6 +352,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
               epi_row(p, rows, tile, c, s_rowf[c], acc, lane);
             }
           }
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
           asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // stores issued, my_part and s_rowf free
           ++sg;
           if (cu.left == 1 && tid == 0) {   // that was this CTA's last segment of the phase
@@ -368,6 +378,8 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
       int it = 0, ready_ph = -1;
       bool issued = false;
       asm volatile("griddepcontrol.wait;" ::: "memory");   // the first phase's planes come from the preceding kernel
+      s_base_gen = ld_acquire_u32(cp.bar_gen);
+      __threadfence_block();
       s_dep_ok = 1;
       while (cu.ph < cp.nphases) {
         if (cu.ph != ready_ph) {
