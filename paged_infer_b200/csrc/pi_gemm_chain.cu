@@ -122,8 +122,109 @@ __device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, con
   return false;
 }
 
+// What the epilogue of a segment needs from its CTA.
+struct EpiCtx {
+  float* my_part;            // [BN][128] shared
+  float* s_rowf;             // [BN] shared
+  int* s_last;               // shared
+  volatile int* s_abort;
+  volatile int* s_dep_ok;
+  uint32_t accum_full, accum_empty;   // mbarriers
+  uint32_t tmem_d;           // accumulator base (lane 0, column 0)
+  int cta;
+};
+
+// The segment of row tile `tile` of phase `ph` that this CTA has just fed to the tensor pipe (`whole`: it covered the
+// tile's entire K range).  All 16 producer warps call this in lock step (it synchronises them with named barrier 1):
+// take the accumulator out of tensor memory as soon as the MMAs are done and release it for the next segment; a whole
+// tile goes through shared memory straight to the epilogue; a partial one goes to its scratch slot in global memory
+// and the CTA that hands in the last partial of the tile adds them in slot (= K) order and runs the epilogue.
+// Out of line on purpose: it runs once per segment and would otherwise be cloned into every slot of the unrolled
+// producer loop.
+template <int BN>
+__device__ __noinline__ void segment_epilogue(const ChainParams& cp, const EpiCtx& e, int ph, int tile, bool whole, int sg) {
+  constexpr int kTileFloats = BN * kBM;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quad = warp & 3, half = (warp >> 2) & 1;
+  const GemmParams& p = cp.ph[ph];
+  const long U = (long)cp.rtiles[ph] * p.nkb;
+  const int act = cp.active[ph];
+  const int c_first = owner_of((long)tile * p.nkb, U, act), c_last = owner_of((long)(tile + 1) * p.nkb - 1, U, act);
+  float* my_part = e.my_part;
+  float* part_dst = whole ? my_part : cp.partials + (size_t)(e.cta + tile) * kTileFloats;
+  if (warp < kParkWarps) {
+    int got = 0;
+    if (lane == 0) {
+      got = (!*e.s_abort && mbar_wait_dep(e.accum_full, (uint32_t)(sg & 1), e.s_dep_ok)) ? 1 : 0;
+      if (!got && !*e.s_abort) {
+        *e.s_abort = 1;
+        if (cp.err_flag) atomicExch(cp.err_flag, 5);
+      }
+    }
+    got = __shfl_sync(0xffffffffu, got, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
+    if (BN >= 32 || half == 0) {
+      const uint32_t my_d = e.tmem_d + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+        float v[16];
+        if (got) {
+          tmem_ld_sum16<BN>(my_d, c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part_dst[(c0 + j) * kBM + quad * 32 + lane] = v[j];
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(e.accum_empty);   // the next segment's MMAs may overwrite the accumulator
+    }
+    if (!whole) __threadfence();
+  }
+  if (tid < BN) e.s_rowf[tid] = act_row_factor(p, tid);
+  EpiRows rows;
+  epi_rows_load(p, tile * kBM, tid, rows);
+  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+  bool finish = true;
+  if (!whole) {   // hand the partial in; whoever hands in the last one of the tile finishes it
+    if (tid == 0) {
+      const unsigned int n = (unsigned int)(c_last - c_first + 1);
+      const unsigned int t = atom_add_acq_rel(cp.tickets + tile, 1u);
+      *e.s_last = (t == n - 1u) ? 1 : 0;
+      if (t == n - 1u) cp.tickets[tile] = 0u;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+    finish = *e.s_last != 0;
+    if (finish) __threadfence();
+  }
+  if (finish) {
+    const int r4 = lane * 4, csub = warp;   // 16 activation rows in flight per pass
+    const int nparts = c_last - c_first + 1;
+    const float* slot0 = cp.partials + (size_t)(c_first + tile) * kTileFloats + r4;
+    for (int c = csub; c < BN; c += kProducerWarps) {
+      float4 acc;
+      if (whole) {
+        acc = *reinterpret_cast<const float4*>(my_part + c * kBM + r4);
+      } else {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int j = 0; j < nparts; ++j) {   // slot order = K order: the same sum whoever adds it up
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(slot0 + (size_t)j * kTileFloats + c * kBM));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      }
+      epi_row(p, rows, tile, c, e.s_rowf[c], acc, lane);
+    }
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
+  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // stores issued, my_part and s_rowf free
+}
+
 template <int BN, int STAGES>
-__global__ void __maxnreg__(112)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant__ ChainMaps maps) {
   constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
   constexpr int kBStageBytes = 2 * kBAtomBytes;
@@ -153,9 +254,10 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   pi_grid_launch_dependents();
 
   // ---- weight producers: the first group of loads goes out before anything else (weights depend on nothing) ----
+  // Rolling prefetch: the 32 bytes of unit i + 4 are requested into the register slot that unit i has just left.
   constexpr int kGroup = 4;
-  uint32_t cur[kGroup][8], nxt[kGroup][8];
-  UnitIter pf;   // prefetch position, up to two groups ahead of the unit being widened
+  uint32_t cur[kGroup][8];
+  UnitIter pf;   // prefetch position, four units ahead of the unit being widened
   pf.ph = 0;
   auto unit_ptr = [&](const UnitIter& u) {
     const GemmParams& p = cp.ph[u.ph];
@@ -239,16 +341,19 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
     if (tid == 0) arrive_upto(cu.ph);   // phases in which this CTA has nothing to do
 
     const uint32_t my_a = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(kq * 16);
-    const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
+    EpiCtx ec;
+    ec.my_part = my_part;
+    ec.s_rowf = s_rowf;
+    ec.s_last = &s_last;
+    ec.s_abort = &s_abort;
+    ec.s_dep_ok = &s_dep_ok;
+    ec.accum_full = accum_full;
+    ec.accum_empty = accum_empty;
+    ec.tmem_d = tmem;
+    ec.cta = cta;
     // Once a wait has run out (s_abort) the warps stop waiting and stop feeding the pipeline, but they still walk
     // their units to the end: the named barriers of the epilogues below must be reached by all 16 warps in lock step.
     while (cu.ph < cp.nphases) {
-#pragma unroll
-      for (int d = 0; d < kGroup; ++d)
-        if (pf.ph < cp.nphases) {
-          ld_stream_32(unit_ptr(pf), &nxt[d][0]);
-          iter_next(pf, cp, cta);
-        }
 #pragma unroll
       for (int d = 0; d < kGroup; ++d) {
         if (cu.ph >= cp.nphases) break;
@@ -257,6 +362,10 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
         uint32_t h[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
+        if (pf.ph < cp.nphases) {
+          ld_stream_32(unit_ptr(pf), &cur[d][0]);
+          iter_next(pf, cp, cta);
+        }
         int ok = 1;
         if (lane == 0) ok = (!s_abort && mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -275,85 +384,11 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
 
         if (iter_seg_last(cu)) {
           // ---- the segment [seg_kb0, cu.kb] of row tile cu.tile is in flight: take its accumulator and finish it ----
-          const int ph = cu.ph, tile = cu.tile;
-          const GemmParams& p = cp.ph[ph];
-          const bool whole = seg_kb0 == 0 && cu.kb == p.nkb - 1;
-          const long U = (long)cp.rtiles[ph] * p.nkb;
-          const int act = cp.active[ph];
-          const int c_first = owner_of((long)tile * p.nkb, U, act), c_last = owner_of((long)(tile + 1) * p.nkb - 1, U, act);
           if (!dep_waited) {
             asm volatile("griddepcontrol.wait;" ::: "memory");   // the epilogue reads what the preceding kernel wrote
             dep_waited = true;
           }
-          float* part_dst = whole ? my_part : cp.partials + (size_t)(cta + tile) * kTileFloats;
-          if (warp < kParkWarps) {
-            int got = 0;
-            if (lane == 0) {
-              got = (!s_abort && mbar_wait_dep(accum_full, (uint32_t)(sg & 1), &s_dep_ok)) ? 1 : 0;
-              if (!got && !s_abort) {
-                s_abort = 1;
-                if (cp.err_flag) atomicExch(cp.err_flag, 5);
-              }
-            }
-            got = __shfl_sync(0xffffffffu, got, 0);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
-            if (BN >= 32 || half == 0) {
-#pragma unroll 1
-              for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
-                float v[16];
-                if (got) {
-                  tmem_ld_sum16<BN>(my_d, c0, v);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) part_dst[(c0 + j) * kBM + quad * 32 + lane] = v[j];
-              }
-              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-              __syncwarp();
-              if (lane == 0) mbar_arrive(accum_empty);   // the next segment's MMAs may overwrite the accumulator
-            }
-            if (!whole) __threadfence();
-          }
-          if (tid < BN) s_rowf[tid] = act_row_factor(p, tid);
-          EpiRows rows;
-          epi_rows_load(p, tile * kBM, tid, rows);
-          asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-          bool finish = true;
-          if (!whole) {   // hand the partial in; whoever hands in the last one of the tile finishes it
-            if (tid == 0) {
-              const unsigned int n = (unsigned int)(c_last - c_first + 1);
-              const unsigned int t = atom_add_acq_rel(cp.tickets + tile, 1u);
-              s_last = (t == n - 1u) ? 1 : 0;
-              if (t == n - 1u) cp.tickets[tile] = 0u;
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-            finish = s_last != 0;
-            if (finish) __threadfence();
-          }
-          if (finish) {
-            const int r4 = lane * 4, csub = warp;   // 16 activation rows in flight per pass
-            const int nparts = c_last - c_first + 1;
-            const float* slot0 = cp.partials + (size_t)(c_first + tile) * kTileFloats + r4;
-            for (int c = csub; c < BN; c += kProducerWarps) {
-              float4 acc;
-              if (whole) {
-                acc = *reinterpret_cast<const float4*>(my_part + c * kBM + r4);
-              } else {
-                acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                for (int j = 0; j < nparts; ++j) {   // slot order = K order: the same sum whoever adds it up
-                  const float4 v = __ldcg(reinterpret_cast<const float4*>(slot0 + (size_t)j * kTileFloats + c * kBM));
-                  acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
-              }
-              epi_row(p, rows, tile, c, s_rowf[c], acc, lane);
-            }
-          }
-          asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
-          asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // stores issued, my_part and s_rowf free
+          segment_epilogue<BN>(cp, ec, cu.ph, cu.tile, seg_kb0 == 0 && cu.kb == cu.nkb - 1, sg);
           ++sg;
           if (cu.left == 1 && tid == 0) {   // that was this CTA's last segment of the phase
             UnitIter nx = cu;
@@ -363,10 +398,6 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
         }
         iter_next(cu, cp, cta);
       }
-#pragma unroll
-      for (int d = 0; d < kGroup; ++d)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) cur[d][i] = nxt[d][i];
     }
     if (tid == 0) arrive_upto(cp.nphases);   // after an abort: keep the barrier consistent for the other CTAs
   } else if (warp == kProducerWarps) {
