@@ -3,26 +3,33 @@
 
 Default workload (`tinyllama_b64_paged`): TinyLlama-1.1B architecture, random-init
 int8 projections (lm_head int8 as well), 64 concurrent sequences with context
-lengths uniform in [256, 2048] (seed 2), KV block size 16, f32 KV; sequences
-0-31 share the physical blocks of a common 512-token prefix, sequences 56-63
-are copy-on-write forks of 48-55; one greedy decode step per sequence per
-engine step.  A "step" is one engine step over all 64 sequences.
+lengths uniform in [256, 2048] (seed 2), KV block size 16, f32 KV.  The batch is
+set up the way the engine would: every prompt is admitted through the C++
+KvCacheManager (chained block hash: sequences 0-31 share the first 512 token
+ids and therefore the same 32 physical blocks), prefilled on the device for the
+part the prefix cache did not cover, published; sequences 56-63 are forks of
+48-55 (same table, copy-on-write split on their first write).  A "step" is one
+engine step: one greedy decode token for each of the 64 sequences.
 
   value      decode tok/s with everything resident on the device: K greedy steps
              inside one `pi_model_decode_multi` call (no host round trip between
              steps), timed with CUDA events.
   e2e        the same metric through the per-step public call
-             (`LlamaWeights.decode_batch_into`): block-table bookkeeping on the
-             host, tokens / tables / positions copied host->device and the
-             chosen ids device->host inside the timed region, every step.
-  roofline   the dominant kernel timed alone with CUDA events.
+             (`LlamaWeights.decode_batch_into`): block bookkeeping by the
+             KvCacheManager on the host (grow, copy-on-write), tokens / tables /
+             positions copied host->device and the chosen ids device->host
+             inside the timed region, every step.
+  roofline   the dominant kernel class timed with CUDA events inside real steps.
   cpu_baseline  the CPU oracle (a C++ restatement of the reference's rayon/AVX2
              path; the reference itself is Rust and cannot be built here) on a
              bounded sample of the same workload, on this box's host cores.
 
 `--impl reference` times that CPU path as the reference arm.  With `--gpus N`
-under torchrun every rank runs its own replica of the workload (sequences are
-independent; no collective on the data path): weak scaling.
+under torchrun every rank first runs its own replica of the workload (sequences
+are independent; no collective on the data path: weak scaling, `value`), then
+all N ranks together run the tensor-parallel workload of the sharded
+configuration (Llama-3-8B architecture, batch 32, context 4096: column-split
+q/k/v/gate/up, row-split o/down with one exchange each) and attach it as `tp`.
 """
 from __future__ import annotations
 
@@ -51,96 +58,83 @@ GEMV_SHAPES = {"q/o 2048x2048": (2048, 2048), "k/v 256x2048": (256, 2048), "qkv 
                "lm_head Llama-3 128256x4096": (128256, 4096)}
 
 
-# ---- host-side block bookkeeping (what KvCacheManager does for this workload) ---------------------------------
-class PagedBatch:
-    """Block tables of the 64-sequence workload: a refcounted free list, prefix
-    sharing at admission, fork = table copy, copy-on-write before a write into a
-    shared block (reference src/memory/allocator.rs, kv_cache_manager.rs:116-345)."""
+# ---- the batch as the engine holds it ---------------------------------------------------------------------------
+class EngineBatch:
+    """The 64 sequences of the workload with their block bookkeeping done by the C++ KvCacheManager
+    (include/paged_infer_memory.hpp behind libpaged_infer_host.so; reference src/memory/kv_cache_manager.rs:116-345):
+    admission with prefix reuse through the chained block hash, publishing, forks, and before every step
+    ``prepare_step`` = Engine::plan_step (src/engine.rs:612-699): grow the mapping, split shared blocks copy-on-write.
+    The tables live in the packed arrays that the device library takes and are updated in place."""
 
-    def __init__(self, seed: int, batch: int, total_steps: int, lo=256, hi=2048, prefix_tokens=512, forks=8):
+    def __init__(self, api, seed: int, batch: int, reserve_steps: int, lo=256, hi=2048, prefix_tokens=512, forks=8, vocab=32000):
+        from paged_infer_b200 import host
         rng = np.random.default_rng(seed)
-        self.batch = batch
         ctx = rng.integers(lo, hi + 1, batch)
         if forks:
             ctx[batch - forks:] = ctx[batch - 2 * forks:batch - forks]   # a fork starts at its parent's length
-        self.lengths = [int(c) for c in ctx]
-        need = sum((c + total_steps + BLOCK - 1) // BLOCK + 1 for c in self.lengths)
-        self.num_blocks = need + 8
-        self.free = list(range(self.num_blocks))[::-1]
-        self.ref = [0] * self.num_blocks
-        self.tables = []
-        self.cow_copies = []          # (src, dst) pairs produced by the last plan()
-        self.total_cow = 0
-        shared = []
-        for b in range(batch):
-            nblk = (self.lengths[b] + BLOCK - 1) // BLOCK
-            if forks and b >= batch - forks:               # fork: same table as the parent, refcounts bumped
-                t = list(self.tables[b - forks])
-                for pb in t:
-                    self.ref[pb] += 1
+        self.batch, self.forks, self.prefix_tokens = batch, forks, prefix_tokens
+        self.lengths = np.array(ctx, np.int32)
+        prefix = rng.integers(0, vocab, prefix_tokens).astype(np.uint32)
+        self.prompts = []
+        for b in range(batch - forks):
+            n = int(ctx[b])
+            if b < batch // 2:   # the first half of the batch opens with the same token ids
+                t = np.concatenate([prefix, rng.integers(0, vocab, max(n - prefix_tokens, 0)).astype(np.uint32)])[:n]
             else:
-                t = []
-                if b < batch // 2:                          # prefix-cache hit on full blocks only
-                    n_shared = min(prefix_tokens // BLOCK, self.lengths[b] // BLOCK)
-                    while len(shared) < n_shared:
-                        shared.append(self._alloc())
-                    for pb in shared[:n_shared]:
-                        self.ref[pb] += 1
-                        t.append(pb)
-                while len(t) < nblk:
-                    t.append(self._alloc())
-            self.tables.append(t)
-        for pb in shared:                                   # the cache's own reference
-            self.ref[pb] += 1
-        self.packed = None                                  # PackedBlockTables mirror, kept in step by plan()
+                t = rng.integers(0, vocab, n).astype(np.uint32)
+            self.prompts.append(t)
+        self.num_blocks = int(sum((int(c) + reserve_steps) // BLOCK + 2 for c in ctx)) + 64
+        self.mgr = host.KvCacheManager(self.num_blocks, BLOCK, True)
+        width = (int(ctx.max()) + reserve_steps) // BLOCK + 4
+        self.packed = api.PackedBlockTables(batch, width) if api is not None else None
+        self.tables = self.packed.mat if api is not None else np.full((batch, width), -1, np.int32)
+        self.lens = self.packed.lens if api is not None else np.zeros(batch, np.int32)
+        self.cow = np.empty((batch, 2), np.int32)
+        self.seq_ids = np.arange(batch, dtype=np.uint64)
+        self.tick = 0
+        self.prefilled_tokens = 0
 
-    def _alloc(self) -> int:
-        pb = self.free.pop()
-        self.ref[pb] = 1
-        return pb
+    def admit_all(self, prefill=None):
+        """Admit, prefill what the prefix cache did not cover (``prefill(tokens, start_pos, table)``; None: bookkeeping
+        only) and publish every prompt, in order; then fork the last sequences from their parents."""
+        for b in range(self.batch - self.forks):
+            prompt = self.prompts[b]
+            cached = self.mgr.admit(b, prompt, self.tick)
+            resume = min(cached, len(prompt) - 1)    # a fully cached prompt still recomputes its last token
+            if prefill is not None:
+                prefill(prompt[resume:], resume, self.mgr.table(b))
+            self.prefilled_tokens += len(prompt) - resume
+            self.mgr.publish_prompt_blocks(b)
+        for i in range(self.forks):
+            self.mgr.fork(self.batch - 2 * self.forks + i, self.batch - self.forks + i, self.tick)
 
-    def plan(self):
-        """Before a step: give every sequence a writable slot for position len(seq)."""
-        self.cow_copies = []
-        for b in range(self.batch):
-            pos, t = self.lengths[b], self.tables[b]
-            lb = pos // BLOCK
-            if lb >= len(t):
-                t.append(self._alloc())
-                if self.packed is not None:
-                    self.packed.append(b, t[-1])
-            elif self.ref[t[lb]] > 1:                       # ensure_writable: copy-on-write split
-                dst = self._alloc()
-                self.cow_copies.append((t[lb], dst))
-                self.ref[t[lb]] -= 1
-                t[lb] = dst
-                if self.packed is not None:
-                    self.packed.remap(b, lb, dst)
-        self.total_cow += len(self.cow_copies)
-        return self.cow_copies
+    def plan(self, ahead: int = 0):
+        """Settle memory for the step that writes position length + ahead of every sequence; -> [(src, dst)] copies."""
+        self.tick += 1
+        pos = (self.lengths + ahead).astype(np.int32)
+        n = self.mgr.prepare_step(self.seq_ids, pos, self.tables, self.lens, self.cow, self.tick)
+        return [(int(self.cow[i, 0]), int(self.cow[i, 1])) for i in range(n)]
 
-    def commit(self):
-        self.lengths = [n + 1 for n in self.lengths]
+    def commit(self, steps: int = 1):
+        self.lengths += steps
 
-    def pack(self, api):
-        """The tables as arrays, from now on updated in place by plan() (what an engine's FFI shim would keep)."""
-        self.packed = api.PackedBlockTables(self.batch, max(len(t) for t in self.tables) + 8)
-        for b, t in enumerate(self.tables):
-            self.packed.set_row(b, t)
-        return self.packed
+    def table_lists(self):
+        return [self.tables[b, :self.lens[b]].tolist() for b in range(self.batch)]
 
     def unique_mapped_tokens(self) -> int:
         """Tokens of KV that one step must read at least once (shared physical blocks count once)."""
         seen = {}
-        for n, t in zip(self.lengths, self.tables):
-            for lb, pb in enumerate(t):
+        for b in range(self.batch):
+            n = int(self.lengths[b])
+            for lb in range(int(self.lens[b])):
                 used = min(BLOCK, n + 1 - lb * BLOCK)
                 if used > 0:
+                    pb = int(self.tables[b, lb])
                     seen[pb] = max(seen.get(pb, 0), used)
         return sum(seen.values())
 
     def logical_tokens(self) -> int:
-        return sum(n + 1 for n in self.lengths)
+        return int((self.lengths + 1).sum())
 
 
 # ---- clocks ---------------------------------------------------------------------------------------------------
@@ -181,19 +175,24 @@ class ClockSampler:
                 "samples": len(rows), "reasons": sorted(reasons)}
 
 
-def measured_peaks():
+def measured_peaks(sustained: bool = False):
+    """(HBM GB/s, dense bf16 TFLOP/s, kind): the driver-measured peaks of this pool, else the stated fallback.  The bf16
+    figure is the burst one for a kernel timed alone, the sustained one for a kernel timed inside a long step."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained" if sustained else "bf16_tflops"]), "measured"
+    return 6650.0, (1400.0 if sustained else 1590.0), "fallback"
 
 
 # ---- the CPU arm (oracle) ---------------------------------------------------------------------------------------
-def cpu_decode_sample(cfg: dict, pb: PagedBatch, budget_s: float, max_steps: int, warmup: int = 1):
-    """Time oracle decode steps of the same 64 sequences on the host cores."""
+def cpu_decode_sample(cfg: dict, eb: EngineBatch, budget_s: float, max_steps: int, warmup: int = 1):
+    """Time oracle decode steps of the same 64 sequences (same tables, from the same KvCacheManager) on the host cores.
+    The thread count is set here to the cores this process may run on, whatever the launcher put in OMP_NUM_THREADS."""
     from oracle import pi_oracle as orc
     orc.build()
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    orc.lib().orc_set_num_threads(int(cores))
     rng = np.random.default_rng(7)
     H, NL, KH = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["num_key_value_heads"]
     hd = H // cfg["num_attention_heads"]
@@ -203,24 +202,25 @@ def cpu_decode_sample(cfg: dict, pb: PagedBatch, budget_s: float, max_steps: int
         return (rng.integers(-127, 128, (rows, cols), dtype=np.int8), np.full(rows, 1.6e-4, np.float32))
 
     shapes = {"wq": (H, H), "wk": (KH * hd, H), "wv": (KH * hd, H), "wo": (H, H), "w1": (inter, H), "w2": (H, inter), "w3": (inter, H)}
-    layer0 = {k: i8(*s) for k, s in shapes.items()}       # timing does not depend on the values: reuse one layer's codes
-    projs = [layer0] * NL
+    projs = [{k: i8(*s) for k, s in shapes.items()} for _ in range(NL)]   # every layer its own codes: 1 GB streamed per step
     embed = rng.integers(0x3B00, 0x3C00, (vocab, H), dtype=np.uint16)  # small positive bf16 values
     ones = np.ones(H, np.float32)
     model = orc.Model(cfg, embed, ones, [ones] * NL, [ones] * NL, projs, i8(vocab, H))
-    layout_floats = NL * pb.num_blocks * BLOCK * KH * 2 * hd
+    layout_floats = NL * eb.num_blocks * BLOCK * KH * 2 * hd
     chunk = rng.standard_normal(1 << 22).astype(np.float32)
-    kv = np.resize(chunk, layout_floats)
-    tokens = rng.integers(0, vocab, pb.batch).astype(np.uint32)
+    kv = np.resize(chunk, layout_floats)     # values do not change the CPU path's timing; the tables are the real ones
+    olayout = orc.kv_layout(NL, eb.num_blocks, BLOCK, KH, hd)
+    tokens = rng.integers(0, vocab, eb.batch).astype(np.uint32)
     times = []
     t_start = time.time()
     for s in range(warmup + max_steps):
-        pb.plan()
         t0 = time.perf_counter()
-        logits = model.decode_batch(tokens, pb.lengths, pb.tables, kv, BLOCK)
+        for src, dst in eb.plan():
+            orc.kv_copy_block(olayout, kv, src, dst)
+        logits = model.decode_batch(tokens, eb.lengths.tolist(), eb.table_lists(), kv, BLOCK)
         tokens = np.array([orc.argmax(r) for r in logits], np.uint32)
         dt = time.perf_counter() - t0
-        pb.commit()
+        eb.commit()
         if s >= warmup:
             times.append(dt)
         if time.time() - t_start > budget_s and len(times) >= 1:
@@ -228,21 +228,37 @@ def cpu_decode_sample(cfg: dict, pb: PagedBatch, budget_s: float, max_steps: int
     return times, orc.num_threads(), orc.backend()
 
 
+def workload_config(eb: EngineBatch, extra: dict) -> dict:
+    """The `config` object both arms print: same keys, same workload."""
+    st = eb.mgr.stats()
+    cfg = {"workload": "tinyllama_b64_paged", "batch_per_gpu": eb.batch, "block_size": BLOCK, "context": "U[256,2048] seed 2",
+           "prefix_shared_sequences": eb.batch // 2, "prefix_tokens": eb.prefix_tokens, "cow_forks": eb.forks,
+           "host_bookkeeping": "C++ KvCacheManager (admit -> prefill tail -> publish -> fork -> prepare_step)",
+           "prefix_cache_hits": st["prefix_hits"], "prefix_tokens_saved": st["prefix_tokens_saved"], "cow_copies": st["cow_copies"],
+           "lm_head": "int8"}
+    cfg.update(extra)
+    return cfg
+
+
 def run_reference_arm(args, rank: int):
     if rank != 0:
         return
     cfg = dict(TINYLLAMA)
-    pb = PagedBatch(2, 64, args.steps + args.warmup + 2)
-    times, threads, backend = cpu_decode_sample(cfg, pb, budget_s=150.0, max_steps=args.steps, warmup=min(args.warmup, 1))
+    W = max(args.warmup, 1)
+    eb = EngineBatch(None, 2, 64, args.steps + W + 4)
+    eb.admit_all(None)
+    times, threads, backend = cpu_decode_sample(cfg, eb, budget_s=150.0, max_steps=args.steps, warmup=W)
     ms = 1e3 * float(np.mean(times))
     val = 64.0 / (ms / 1e3)
-    sample = (f"{len(times)} of the requested {args.steps} steps (time-bounded), each a full 64-sequence engine step "
-              f"(contexts U[256,2048], block 16) on the CPU oracle, {backend}, {threads} threads")
+    sample = (f"{len(times)} of the requested {args.steps} steps (time-bounded, {W} warm-up), each a full 64-sequence engine step "
+              f"(contexts U[256,2048], block 16, 22 distinct layers of int8 codes) on the CPU oracle, {backend}, {threads} threads")
     line = {
         "impl": "reference", "metric": "int8 batched paged decode throughput (TinyLlama-1.1B arch, 64 sequences)",
-        "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1),
+        "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": len(times), "warmup": W,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights, f32 activations/accumulate/KV",
-        "data": "synthetic", "config": {"workload": "tinyllama_b64_paged", "batch": 64, "block_size": BLOCK, "context": "U[256,2048] seed 2"},
+        "data": "synthetic",
+        "config": workload_config(eb, {"weights": "uniform int8 codes, 22 distinct layers", "kv": "N(0,1) fill (timing does not depend on the values)",
+                                       "parallelism": "host cores"}),
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference is a Rust crate and cannot be built on this box (no cargo/rustc); this arm is its C++ restatement (oracle/)",
@@ -287,6 +303,89 @@ def gemv_sweep(api, ctx, torch, hbm_peak, reps=3):
     return out
 
 
+def config1_sweep(api, ctx, torch, hbm_peak, bf16_peak, reps=3):
+    """The isolated projection sweep of the second configuration: every TinyLlama projection shape at 1, 8, 32, 128
+    and 512 activation rows.  Weight copies rotate so that every launch streams its weights from HBM; launches go
+    back to back with one CUDA-event pair around the train.  Up to 32 rows the figure is GB/s over the algorithmic
+    bytes (HBM bound); from 128 rows on it is useful TFLOP/s (2*M*N*K) against the measured bf16 peak - the tensor
+    pipe does three times that work because every f32 activation travels as three bf16 planes."""
+    out = {}
+    rng = np.random.default_rng(1)
+    shapes = {k: v for k, v in GEMV_SHAPES.items() if "Llama-3" not in k and "fused" not in k}
+    for name, (N, K) in shapes.items():
+        bytes_w = N * K + 4 * N
+        copies = int(min(24, max(2, -(-(300 << 20) // bytes_w))))
+        q = rng.integers(-127, 128, (N, K), dtype=np.int8)
+        sc = np.full(N, 1.6e-4, np.float32)
+        lins = [api.Projection.int8(ctx, q, sc) for _ in range(copies)]
+        row = {}
+        for M in (1, 8, 32, 128, 512):
+            x = torch.randn(M, K, device="cuda", dtype=torch.float32)
+            y = torch.empty(M, N, device="cuda", dtype=torch.float32)
+            for l in lins:
+                l.apply_device(x, y, M)
+            torch.cuda.synchronize()
+            best = None
+            rounds = 2 if M >= 128 else 4
+            for _ in range(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _r in range(rounds):
+                    for l in lins:
+                        l.apply_device(x, y, M)
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (rounds * copies)
+                best = us if best is None else min(best, us)
+            algo = N * K + 4 * N + 4 * M * K + 4 * M * N
+            ent = {"us": round(best, 2), "GB/s": round(algo / best / 1e3, 1), "frac_of_hbm_peak": round(algo / best / 1e3 / hbm_peak, 3)}
+            if M >= 128:
+                tf = 2.0 * M * N * K / best / 1e6
+                ent.update({"useful_TFLOP/s": round(tf, 1), "frac_of_bf16_peak": round(tf / bf16_peak, 3),
+                            "tensor_TFLOP/s_with_3_planes": round(3 * tf, 1)})
+            row[f"M={M}"] = ent
+        out[name] = row
+        for l in lins:
+            l.close()
+    return out
+
+
+def prefill_70b_shape(api, ctx, torch, layers=2):
+    """The prefill batch of the 70B configuration - 8 prompts of 2048 tokens at hidden 8192, 64 query / 8 KV heads of
+    128, FFN 28672 - on a model cut to `layers` layers (one GPU holds them; the full model is 80 of the same), chunks
+    of 512 positions.  Device-generated int8 weights."""
+    from paged_infer_b200.loader import LlamaConfig
+    arch = dict(LLAMA2_70B)
+    arch["num_hidden_layers"] = layers
+    cfg = LlamaConfig(**arch, quantization="int8")
+    model = api.LlamaWeights.synthetic(ctx, cfg, seed=4, std=0.02, max_batch=512, max_positions=2048 + 16)
+    n_prompt, prompts, chunk = 2048, 8, 512
+    nbp = n_prompt // BLOCK + 1
+    kv = api.KvCache(ctx, model.kv_layout(prompts * nbp, BLOCK))
+    rng = np.random.default_rng(4)
+    toks = [rng.integers(0, cfg.vocab_size, n_prompt).astype(np.uint32) for _ in range(prompts)]
+    tabs = [list(range(i * nbp, (i + 1) * nbp)) for i in range(prompts)]
+    model.prefill_batched(toks[0], 0, tabs[0], kv, chunk)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t, tab in zip(toks, tabs):
+        model.prefill_batched(t, 0, tab, kv, chunk)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    layer_weights = model.weight_bytes() - cfg.vocab_size * cfg.hidden_size - 4 * cfg.vocab_size
+    H, hd = cfg.num_attention_heads, cfg.head_dim
+    flops = prompts * (2.0 * n_prompt * layer_weights + 4.0 * layers * H * hd * n_prompt * (n_prompt + 1) / 2)
+    out = {"layers": layers, "of_layers": 80, "prompts": prompts, "prompt_tokens": n_prompt, "chunk": chunk, "ms": round(ms, 2),
+           "tok/s_at_this_depth": round(prompts * n_prompt / (ms / 1e3), 1), "ms_per_layer_per_prompt": round(ms / layers / prompts, 3),
+           "useful_TFLOP/s": round(flops / (ms / 1e3) / 1e12, 1),
+           "attention": "head_dim 128: shared-table kernel on mma.sync TF32x3 (the tcgen05 one covers head_dim 64)"}
+    kv.close()
+    model.close()
+    return out
+
+
 def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -297,33 +396,19 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    hbm_peak, peak_kind = measured_peaks()
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
     cfgd = dict(TINYLLAMA)
     cfg = LlamaConfig(**cfgd, quantization="int8")
     K, W = args.steps, max(args.warmup, 3)
     B = 64
+    P = min(K, 8)
 
     # A stream of our own (torch's default stream has handle 0, which the library reads as "create one").
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(local_rank, stream=tstream.cuda_stream)
-    model = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=B, max_positions=4096)
+    model = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=512, max_positions=4096)
     weight_bytes = model.weight_bytes()
-
-    # --- resident run: K steps in one call -------------------------------------------------------------------
-    pb = PagedBatch(2 + rank, B, 2 * (K + W) + 4)
-    kv = api.KvCache(ctx, model.kv_layout(pb.num_blocks, BLOCK))
-    kv.fill_normal(1234 + rank, 1.0)
-    rng = np.random.default_rng(100 + rank)
-    tokens = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
-
-    def reserve(steps):  # pre-extend the tables so that `steps` device-side steps have writable slots
-        saved = list(pb.lengths)
-        for _ in range(steps):
-            for src, dst in pb.plan():
-                kv.copy_block(src, dst)
-            pb.commit()
-        pb.lengths = saved
 
     def barrier():
         torch.cuda.synchronize()
@@ -331,21 +416,58 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # --- the batch, set up as the engine would: the same on every rank (same seed: replicas of one workload) ---------
+    eb = EngineBatch(api, 2, B, 2 * (K + W) + P + 8, vocab=cfg.vocab_size)
+    kv = api.KvCache(ctx, model.kv_layout(eb.num_blocks, BLOCK))
+    t0 = time.time()
+    eb.admit_all(lambda toks, start, table: model.prefill_batched(toks, start, table, kv, 512))
+    torch.cuda.synchronize()
+    setup_prefill_s = time.time() - t0
+    rng = np.random.default_rng(100)
+    tokens = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
+
+    # --- end to end: one public call per step, host bookkeeping + copies inside the timed region --------------------
+    def e2e_step(tok):
+        for src, dst in eb.plan():
+            kv.copy_block(src, dst)
+        ids = model.decode_batch_into(tok, eb.lengths, eb.packed, kv, want_logits=False, want_argmax=True)
+        eb.commit()
+        return ids
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(W):
+        tokens = e2e_step(tokens)
+    barrier()
+    e0.record()
+    for _ in range(K):
+        tokens = e2e_step(tokens)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    mb = int(eb.lens.max())
+    h2d = B * mb * 4 + 3 * B * 4 + B * 4
+    d2h = B * 4
+
+    # --- resident run: K steps in one call ----------------------------------------------------------------------------
+    def reserve(steps):  # pre-extend the tables so that `steps` device-side steps have writable slots
+        for s in range(steps):
+            for src, dst in eb.plan(ahead=s):
+                kv.copy_block(src, dst)
+
     reserve(W + K)
-    out = model.decode_multi(tokens, pb.lengths, pb.tables, kv, W)       # warm-up steps
+    out = model.decode_multi(tokens, eb.lengths, eb.packed, kv, W)       # warm-up steps
     tokens = out[-1].copy()
-    pb.lengths = [n + W for n in pb.lengths]
-    kv_tokens_unique = pb.unique_mapped_tokens()
-    kv_tokens_logical = pb.logical_tokens()
+    eb.commit(W)
+    kv_tokens_unique = eb.unique_mapped_tokens()
+    kv_tokens_logical = eb.logical_tokens()
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.3)
     barrier()
     ctx.reset_kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.time()
     e0.record()
-    out = model.decode_multi(tokens, pb.lengths, pb.tables, kv, K)
+    out = model.decode_multi(tokens, eb.lengths, eb.packed, kv, K)
     e1.record()
     barrier()
     t_wall1 = time.time()
@@ -353,59 +475,35 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     resident_ms = e0.elapsed_time(e1)
     clocks = sampler.stop(t_wall0, t_wall1)
     tokens = out[-1].copy()
-    pb.lengths = [n + K for n in pb.lengths]
+    eb.commit(K)
 
-    # --- end to end: one public call per step, host bookkeeping + copies inside the timed region -----------------
-    pb2 = PagedBatch(2 + rank, B, 2 * (K + W) + 4)
-    pb2.pack(api)
-    kv2 = kv  # same pool size and contents distribution; tables index the same physical range
-    tok2 = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
-    h2d = d2h = 0
-
-    def e2e_step(tok):
-        for src, dst in pb2.plan():
-            kv2.copy_block(src, dst)
-        ids = model.decode_batch_into(tok, pb2.lengths, pb2.packed, kv2, want_logits=False, want_argmax=True)
-        pb2.commit()
-        return ids
-
-    for _ in range(W):
-        tok2 = e2e_step(tok2)
-    barrier()
-    e0.record()
-    for _ in range(K):
-        tok2 = e2e_step(tok2)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    mb = max(len(t) for t in pb2.tables)
-    h2d = B * mb * 4 + 3 * B * 4 + B * 4
-    d2h = B * 4
-
-    times = torch.tensor([resident_ms, e2e_ms], device="cuda", dtype=torch.float64)
+    mine = torch.tensor([resident_ms, e2e_ms], device="cuda", dtype=torch.float64)
+    per_rank = [mine.clone() for _ in range(world)]
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    resident_ms, e2e_ms = float(times[0]), float(times[1])
+        dist.all_gather(per_rank, mine)
+    resident_all = [float(t[0]) for t in per_rank]
+    e2e_all = [float(t[1]) for t in per_rank]
+    resident_ms, e2e_ms = max(resident_all), max(e2e_all)
 
-    # --- dominant kernel alone (rank 0) ----------------------------------------------------------------------------
-    roof = other = gemv = cpu = profile_shares = None
-    batch1 = prefill = None
+    # --- kernel classes inside real steps, and the other configurations (rank 0) ------------------------------------
+    roof = other = sweep = gemv = cpu = profile_shares = None
+    batch1 = prefill = prefill70 = None
     if rank == 0:
         H, hd, KH, NL = cfg.num_attention_heads, cfg.head_dim, cfg.num_key_value_heads, cfg.num_hidden_layers
         # Every launch of P real decode steps bracketed by CUDA events on the launching stream.
-        P = min(K, 8)
         reserve(P)
         ctx.profile_begin()
-        out = model.decode_multi(tokens, pb.lengths, pb.tables, kv, P)
+        out = model.decode_multi(tokens, eb.lengths, eb.packed, kv, P)
         prof = ctx.profile_end()
-        pb.lengths = [n + P for n in pb.lengths]
+        eb.commit(P)
         total_ms = sum(ms for ms, _ in prof.values()) or 1e-9
-        kv_bytes_layer = pb.unique_mapped_tokens() * KH * 2 * hd * 4
+        kv_bytes_layer = eb.unique_mapped_tokens() * KH * 2 * hd * 4
         algo = {"attention": kv_bytes_layer + 2 * B * H * hd * 4,
                 "gemv": weight_bytes / max(prof["gemv"][1] / P, 1), "gemm_tc": weight_bytes / max(prof["gemm_tc"][1] / P, 1)}
         names = {"attention": "attn_decode_v3_kernel<64,8,3> (+ split merge): one layer, 64 sequences",
-                 "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step (average over the 5 matrices per layer)",
-                 "gemm_tc": "gemm_ta_kernel<64,4> (+ the activation splits left): tcgen05 dequant projections of the step (average over its 89 launches)"}
+                 "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step",
+                 "gemm_tc": "gemm_chain_kernel<64,4>: the step's tcgen05 dequant projections, up to four consecutive ones "
+                            "(o, gate/up, down, next q/k/v or the LM head) as phases of one persistent launch"}
         rl = {}
         for cls in ("attention", "gemv", "gemm_tc"):
             ms, n = prof[cls]
@@ -424,11 +522,16 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                        "share_of_step_device_time": round(ms / total_ms, 3), "peak_kind": f"of {peak_kind}",
                        "timing": f"CUDA events around each of {n} launches inside {P} decode steps give the class's share; "
                                  "x the CUDA-event step time of the timed region / launches per step"}
+            if cls == "gemm_tc":   # the same launches against the tensor roof: three bf16 planes per f32 activation
+                rows_total = NL * (3 * cfg.hidden_size + 2 * KH * hd + 2 * cfg.intermediate_size) + cfg.vocab_size
+                tf = 3 * 2.0 * B * (weight_bytes - 4 * rows_total) / (n / P) / us / 1e6
+                rl[cls]["tensor_TFLOP/s_with_3_planes"] = round(tf, 1)
+                rl[cls]["frac_of_bf16_sustained_peak"] = round(tf / measured_peaks(sustained=True)[1], 3)
         order = sorted(rl, key=lambda c: -rl[c]["share_of_step_device_time"])
         roof = rl[order[0]] if order else None
         other = [rl[c] for c in order[1:]]
         profile_shares = {c: round(ms / total_ms, 3) for c, (ms, _) in prof.items() if ms > 0}
-        gemv = gemv_sweep(api, ctx, torch, hbm_peak)
+        kv.close()
 
         # batch-1 decode (config 0 shape): 128 greedy steps from position 128
         t1 = [list(range(0, 17))]
@@ -444,22 +547,22 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         bytes1 = weight_bytes + (128 + 64 + 1) * KH * 2 * hd * 4 * NL
         batch1 = {"tok/s": round(1e3 / ms1, 1), "ms_per_step": round(ms1, 4), "roofline_tok/s": round(hbm_peak * 1e9 / bytes1, 1),
                   "frac_of_hbm_roofline": round((bytes1 / (ms1 / 1e3)) / (hbm_peak * 1e9), 3), "bytes_per_step": bytes1}
+        kvb1.close()
 
-        # prefill (config 0: 128-token prompt; config 4 style: 2048-token prompt), a model instance with room for
-        # 512-position chunks; the chunk's attention runs in the shared-table kernel from 256 positions on
-        prefill = {}
-        pmodel = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=512, max_positions=4096)
+        # prefill (config 0: 128-token prompt; a 2048-token prompt in 512-position chunks)
+        prefill = {"batch_setup": {"tokens_prefilled": eb.prefilled_tokens, "s": round(setup_prefill_s, 2),
+                                   "note": "the 56 prompts of the default workload, prefix hits skipped, chunk 512, host loop included"}}
         for n_prompt, chunk in ((128, 128), (2048, 512)):
             nbp = n_prompt // BLOCK + 1
-            kvp = api.KvCache(ctx, pmodel.kv_layout(nbp, BLOCK))
+            kvp = api.KvCache(ctx, model.kv_layout(nbp, BLOCK))
             prompt = np.random.default_rng(7).integers(0, cfg.vocab_size, n_prompt).astype(np.uint32)
             tab = list(range(nbp))
-            pmodel.prefill_batched(prompt, 0, tab, kvp, chunk)
+            model.prefill_batched(prompt, 0, tab, kvp, chunk)
             torch.cuda.synchronize()
             reps = 3
             e0.record()
             for _ in range(reps):
-                pmodel.prefill_batched(prompt, 0, tab, kvp, chunk)
+                model.prefill_batched(prompt, 0, tab, kvp, chunk)
             e1.record()
             torch.cuda.synchronize()
             msp = e0.elapsed_time(e1) / reps
@@ -467,14 +570,28 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
             prefill[f"prompt{n_prompt}_chunk{chunk}"] = {"tok/s": round(n_prompt / (msp / 1e3), 1), "ms": round(msp, 3),
                                                         "useful_TFLOP/s": round(flops / (msp / 1e3) / 1e12, 1)}
             kvp.close()
-        pmodel.close()
+        model.close()
+        sweep = config1_sweep(api, ctx, torch, hbm_peak, bf16_peak)
+        gemv = gemv_sweep(api, ctx, torch, hbm_peak)
+        prefill70 = prefill_70b_shape(api, ctx, torch)
 
         if world == 1 and not args.no_cpu:
-            pbc = PagedBatch(2, B, 16)
-            ts, threads, backend = cpu_decode_sample(cfgd, pbc, budget_s=20.0, max_steps=4)
+            ebc = EngineBatch(None, 2, B, 16)
+            ebc.admit_all(None)
+            ts, threads, backend = cpu_decode_sample(cfgd, ebc, budget_s=20.0, max_steps=4)
             cms = float(np.mean(ts))
             cpu = {"value": round(B / cms, 2), "unit": "tok/s", "cores": threads, "kind": "port",
                    "sample": f"{len(ts)} full 64-sequence engine steps (same contexts and tables) on the CPU oracle, {backend}, {threads} threads"}
+    else:
+        kv.close()
+        model.close()
+    ctx.close()
+
+    # --- the sharded configuration over the same ranks -----------------------------------------------------------------
+    tp = None
+    if world > 1:
+        barrier()
+        tp = tp_decode(args, "llama3_8b_tp", rank, world, local_rank, min(K, 16), W, with_tp1=True)
 
     if rank == 0:
         step_ms = resident_ms / K
@@ -485,13 +602,13 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
             "value": world * B * K / (resident_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 weights, f32 activations/accumulate/KV", "data": "synthetic",
-            "config": {"workload": "tinyllama_b64_paged", "batch_per_gpu": B, "block_size": BLOCK, "context": "U[256,2048] seed 2",
-                       "prefix_shared_sequences": 32, "prefix_tokens": 512, "cow_forks": 8, "cow_copies": pb.total_cow + pb2.total_cow,
-                       "lm_head": "int8", "weights": "N(0,0.02) generated on device, seed 0", "kv": "N(0,1) fill",
-                       "parallelism": f"dp{world} (independent replicas, sequences sharded, no collective)" if world > 1 else "single GPU",
-                       "l2": "inputs (1.04 GB weights + KV) are larger than L2; no flush needed"},
+            "config": workload_config(eb, {"weights": "N(0,0.02) generated on device, seed 0",
+                                           "kv": "written by prefill of the 56 prompts (random token ids, seed 2)",
+                                           "parallelism": f"dp{world} (independent replicas of the same batch, no collective)" if world > 1 else "single GPU",
+                                           "l2": "inputs (1.04 GB weights + KV) are larger than L2; no flush needed"}),
             "e2e": {"value": world * B * K / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / K},
+            "per_rank_ms_per_step": {"resident": [round(t / K, 4) for t in resident_all], "e2e": [round(t / K, 4) for t in e2e_all]},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roof, "roofline_other": other, "device_time_shares": profile_shares,
@@ -499,7 +616,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                               "kv_tokens_unique": kv_tokens_unique, "kv_tokens_logical": kv_tokens_logical,
                               "achieved_GB/s": round(step_bytes / (step_ms / 1e3) / 1e9, 1), "peak_GB/s": hbm_peak,
                               "frac": round(step_bytes / (step_ms / 1e3) / 1e9 / hbm_peak, 3), "peak_kind": f"of {peak_kind}"},
-            "gemv_m1": gemv, "batch1_decode": batch1, "prefill": prefill, "cpu_baseline": cpu,
+            "config1_sweep": sweep, "gemv_m1": gemv, "batch1_decode": batch1, "prefill": prefill, "prefill_70b_shape": prefill70, "cpu_baseline": cpu,
+            "tp": tp,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -520,10 +638,10 @@ TP_WORKLOADS = {
 }
 
 
-def run_tp_workload(args, rank: int, world: int, local_rank: int):
-    """`--workload llama3_8b_tp`: Llama-3-8B architecture, int8 projections, batch 32 decode at context 4096;
-    `--workload llama2_70b_tp`: Llama-2-70B architecture, batch 64, contexts U[1024,4096] (needs >= 2 GPUs).
-    Tensor-parallel over all `world` ranks (strong scaling: the total work is fixed)."""
+def tp_decode(args, workload: str, rank: int, world: int, local_rank: int, K: int, W: int, with_tp1: bool = False):
+    """One tensor-parallel decode measurement over the `world` ranks of an initialised process group (strong scaling:
+    the total work is fixed).  Returns the result on rank 0, None elsewhere.  `with_tp1`: rank 0 also runs the same
+    workload alone on its GPU, for the speed-up."""
     import torch
     import torch.distributed as dist
 
@@ -531,15 +649,9 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
     from paged_infer_b200.loader import LlamaConfig
     from paged_infer_b200.tp import enable_peer_exchange, exchange_unique_id
 
-    torch.cuda.set_device(local_rank)
-    ident = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        ident = exchange_unique_id(api.nccl_unique_id, dist)
-    hbm_peak, peak_kind = measured_peaks()
-    arch, model_name, B, ctx_spec, seed = TP_WORKLOADS[args.workload]
+    hbm_peak, _, peak_kind = measured_peaks()
+    arch, model_name, B, ctx_spec, seed = TP_WORKLOADS[workload]
     cfg = LlamaConfig(**arch, quantization="int8")
-    K, W = args.steps, max(args.warmup, 3)
     rng = np.random.default_rng(seed)
     if isinstance(ctx_spec, tuple):
         ctx_len = [int(c) for c in rng.integers(ctx_spec[0], ctx_spec[1] + 1, B)]    # identical on every rank
@@ -548,73 +660,114 @@ def run_tp_workload(args, rank: int, world: int, local_rank: int):
         ctx_len = [ctx_spec] * B
         ctx_text = str(ctx_spec)
     CTX = max(ctx_len)
-    tstream = torch.cuda.Stream()
-    torch.cuda.set_stream(tstream)
-    ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank, tp=world, nccl_id=ident)
-    exchange = "single GPU"
-    if world > 1:
-        exchange = "nccl all-reduce"
-        if not args.nccl_exchange:
-            enable_peer_exchange(ctx, B * cfg.hidden_size, dist)
-            exchange = "peer memory (P2P loads + flags, residual add folded in)"
-    model = api.LlamaWeights.synthetic(ctx, cfg, seed=seed, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
+    tokens0 = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)   # identical on every rank
     nblk = [(c + K + W + BLOCK) // BLOCK + 1 for c in ctx_len]
     first = np.concatenate([[0], np.cumsum(nblk)]).astype(int)
-    kv = api.KvCache(ctx, model.kv_layout(int(first[-1]), BLOCK))
-    kv.fill_normal(77 + rank, 1.0)
     tables = [list(range(int(first[b]), int(first[b + 1]))) for b in range(B)]
-    tokens = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)   # identical on every rank
-    pos = list(ctx_len)
 
-    def barrier():
+    def barrier(group_world):
         torch.cuda.synchronize()
-        if world > 1:
+        if group_world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    out = model.decode_multi(tokens, pos, tables, kv, W)
-    tokens, pos = out[-1].copy(), [p + W for p in pos]
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    time.sleep(0.3)
-    barrier()
-    ctx.reset_kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.time()
-    e0.record()
-    out = model.decode_multi(tokens, pos, tables, kv, K)
-    e1.record()
-    barrier()
-    t1 = time.time()
-    launches = ctx.kernel_launches()
-    clocks = sampler.stop(t0, t1)
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms[0])
-    # one profiled pass for the per-class shares (rank 0's view)
-    ctx.profile_begin()
-    model.decode_multi(out[-1].copy(), [p + K for p in pos], tables, kv, 2)
-    prof = ctx.profile_end()
-    if rank == 0:
+    def measure(tp: int, nccl_exchange: bool):
+        ident = exchange_unique_id(api.nccl_unique_id, dist) if tp > 1 else None
+        tstream = torch.cuda.Stream()
+        torch.cuda.set_stream(tstream)
+        ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank if tp > 1 else 0, tp=tp, nccl_id=ident)
+        exchange = "single GPU"
+        if tp > 1:
+            exchange = "nccl all-reduce"
+            if not nccl_exchange:
+                enable_peer_exchange(ctx, B * cfg.hidden_size, dist)
+                exchange = "peer memory (P2P loads + flags, residual add folded in)"
+        model = api.LlamaWeights.synthetic(ctx, cfg, seed=seed, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
+        kv = api.KvCache(ctx, model.kv_layout(int(first[-1]), BLOCK))
+        kv.fill_normal(77 + (rank if tp > 1 else 0), 1.0)
+        pos = list(ctx_len)
+        out = model.decode_multi(tokens0, pos, tables, kv, W)
+        tokens, pos = out[-1].copy(), [p + W for p in pos]
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        time.sleep(0.3)
+        barrier(tp)
+        ctx.reset_kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        out = model.decode_multi(tokens, pos, tables, kv, K)
+        e1.record()
+        barrier(tp)
+        t1 = time.time()
+        launches = ctx.kernel_launches()
+        clocks = sampler.stop(t0, t1)
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if tp > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = float(ms[0])
+        # one profiled pass for the per-class shares (this rank's view)
+        ctx.profile_begin()
+        model.decode_multi(out[-1].copy(), [p + K for p in pos], tables, kv, 2)
+        prof = ctx.profile_end()
         total = sum(v[0] for v in prof.values()) or 1e-9
         weight_bytes = model.weight_bytes()                         # this rank's shard
-        kv_bytes = sum(c + W + K // 2 for c in ctx_len) * (cfg.num_key_value_heads // world) * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
+        kv_bytes = sum(c + W + K // 2 for c in ctx_len) * (cfg.num_key_value_heads // tp) * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
         step_ms = ms / K
+        res = {"tp": tp, "ms_per_step": round(step_ms, 4), "tok/s": round(B * K / (ms / 1e3), 1), "steps": K, "exchange": exchange,
+               "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if tp > 1 else 0, "gpu_launches": launches, "clocks": clocks,
+               "step_roofline": {"bytes_per_step_per_gpu": weight_bytes + kv_bytes, "weight_bytes_per_gpu": weight_bytes,
+                                 "kv_bytes_per_gpu": kv_bytes, "achieved_GB/s_per_gpu": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9, 1),
+                                 "peak_GB/s": hbm_peak, "frac": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9 / hbm_peak, 3),
+                                 "peak_kind": f"of {peak_kind}"},
+               "device_time_shares": {c: round(v[0] / total, 3) for c, v in prof.items() if v[0] > 0}}
+        if tp > 1:
+            dist.barrier()       # peers read each other's buffers: nobody tears down before everyone is done
+        kv.close()
+        model.close()
+        ctx.close()
+        return res
+
+    main = measure(world, args.nccl_exchange)
+    tp1 = None
+    if with_tp1 and world > 1:
+        if rank == 0:
+            tp1 = measure(1, False)
+        dist.barrier()
+    if rank != 0:
+        return None
+    out = {"metric": f"int8 batched paged decode throughput ({model_name} arch, batch {B}, context {ctx_text}, tensor parallel)",
+           "workload": workload, "scaling": "strong", "batch": B, "context": ctx_text, "block_size": BLOCK,
+           "weights": f"N(0,0.02) generated on device, seed {seed}", "kv": "N(0,1) fill"}
+    out.update(main)
+    if tp1 is not None:
+        out["tp1"] = {k: tp1[k] for k in ("ms_per_step", "tok/s", "step_roofline", "device_time_shares")}
+        out["speedup_over_tp1"] = round(tp1["ms_per_step"] / main["ms_per_step"], 3)
+    return out
+
+
+def run_tp_workload(args, rank: int, world: int, local_rank: int):
+    """`--workload llama3_8b_tp`: Llama-3-8B architecture, int8 projections, batch 32 decode at context 4096;
+    `--workload llama2_70b_tp`: Llama-2-70B architecture, batch 64, contexts U[1024,4096] (needs >= 2 GPUs).
+    Tensor-parallel over all `world` ranks (strong scaling: the total work is fixed)."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    K, W = args.steps, max(args.warmup, 3)
+    res = tp_decode(args, args.workload, rank, world, local_rank, K, W, with_tp1=False)
+    if rank == 0:
         line = {
-            "metric": f"int8 batched paged decode throughput ({model_name} arch, batch {B}, context {ctx_text}, tensor parallel)",
-            "value": B * K / (ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": step_ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "metric": res["metric"], "value": res["tok/s"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 weights, f32 activations/accumulate/KV", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": B, "context": ctx_text, "block_size": BLOCK, "parallelism": f"tp{world}",
-                       "collectives_per_step": 2 * cfg.num_hidden_layers + 1 if world > 1 else 0, "exchange": exchange,
-                       "weights": f"N(0,0.02) generated on device, seed {seed}", "kv": "N(0,1) fill"},
-            "gpu_launches": launches, "clocks": clocks,
-            "step_roofline": {"bytes_per_step_per_gpu": weight_bytes + kv_bytes, "weight_bytes_per_gpu": weight_bytes,
-                              "kv_bytes_per_gpu": kv_bytes, "achieved_GB/s_per_gpu": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9, 1),
-                              "peak_GB/s": hbm_peak, "frac": round((weight_bytes + kv_bytes) / (step_ms / 1e3) / 1e9 / hbm_peak, 3),
-                              "peak_kind": f"of {peak_kind}"},
-            "device_time_shares": {c: round(v[0] / total, 3) for c, v in prof.items() if v[0] > 0},
+            "config": {"workload": args.workload, "batch": res["batch"], "context": res["context"], "block_size": BLOCK,
+                       "parallelism": f"tp{world}", "collectives_per_step": res["collectives_per_step"], "exchange": res["exchange"],
+                       "weights": res["weights"], "kv": res["kv"]},
+            "gpu_launches": res["gpu_launches"], "clocks": res["clocks"], "step_roofline": res["step_roofline"],
+            "device_time_shares": res["device_time_shares"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -676,6 +829,27 @@ def run_kernel_case(args):
         e1.record()
         torch.cuda.synchronize()
         algo = B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 + 2 * qv.numel() * 4
+    elif case == "decode_chain":
+        # a two-layer cut of the default model, 64 sequences at 512 tokens: a few whole decode steps, whose projections
+        # leave as persistent chain launches (q/k/v | o, gate/up, down, q/k/v | o, gate/up, down, LM head)
+        cfgd = dict(TINYLLAMA)
+        cfgd["num_hidden_layers"] = 2
+        cfg = LlamaConfig(**cfgd, quantization="int8")
+        model = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=64, max_positions=1024)
+        B, ctx_len = 64, 512
+        nblk = ctx_len // BLOCK + 2
+        kv = api.KvCache(ctx, model.kv_layout(B * nblk, BLOCK))
+        kv.fill_normal(9, 1.0)
+        tables = [list(range(b * nblk, (b + 1) * nblk)) for b in range(B)]
+        tok = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
+        model.decode_multi(tok, [ctx_len] * B, tables, kv, 2)
+        torch.cuda.synchronize()
+        e0.record()
+        for r in range(reps):
+            model.decode_multi(tok, [ctx_len] * B, tables, kv, 1)
+        e1.record()
+        torch.cuda.synchronize()
+        algo = model.weight_bytes() + B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
     elif case == "attention_prefill":
         # the last 512-position chunk of a 2048-token prompt: every entry maps the same table
         cfg = LlamaConfig(**TINYLLAMA, quantization="int8")
@@ -706,7 +880,7 @@ def run_kernel_case(args):
     else:
         raise SystemExit(f"unknown kernel case {case}")
     us = e0.elapsed_time(e1) * 1e3 / reps
-    hbm_peak, peak_kind = measured_peaks()
+    hbm_peak, _, peak_kind = measured_peaks()
     print(json.dumps({"kernel_case": case, "launch_groups": reps, "us_per_launch_group": round(us, 2),
                       "algorithmic_bytes": int(algo), "GB/s": round(algo / us / 1e3, 1),
                       "frac_of_hbm_peak": round(algo / us / 1e3 / hbm_peak, 3), "peak_kind": f"of {peak_kind}"}), flush=True)
@@ -715,7 +889,7 @@ def run_kernel_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel-case", default=None,
-                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention", "attention_prefill"],
+                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention", "attention_prefill", "decode_chain"],
                     help="run a few launches of one kernel on a small case (for a profiler) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -725,10 +899,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--nccl-exchange", action="store_true", help="llama3_8b_tp: all-reduce through NCCL instead of the peer-memory kernel")
     args = ap.parse_args()
-    # stdout carries exactly one JSON line: NCCL's own banner ("NCCL version ...") goes to stderr
+    # stdout carries exactly one JSON line: whatever NCCL logs goes to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

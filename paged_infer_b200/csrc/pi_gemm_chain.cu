@@ -8,10 +8,14 @@
 //
 //   * every phase's work is its (row tile, K block) units in row-tile-major order, cut into equal contiguous shares,
 //     one per CTA - a wide matrix ([gate;up]: 88 row tiles) and a narrow one (o, down: 16) both keep all SMs busy;
-//   * a CTA's share is a few "segments" (a K range of one row tile).  A segment that covers a tile's whole K range
-//     goes straight to the epilogue; otherwise the raw partial tile goes to a scratch slot in global memory and
-//     the CTA that hands in the LAST partial of the tile adds all of them IN SLOT ORDER and runs the epilogue, so
-//     the result does not depend on timing and nobody ever waits for a peer;
+//   * a CTA's share is a few "segments" (a K range of one row tile).  Each segment has an accumulator of its own in
+//     tensor memory (the three bf16 planes of the activations accumulate into the SAME columns, so a segment needs
+//     only as many columns as there are activation rows), so the tensor pipe runs through the whole share without
+//     waiting for an epilogue; the accumulators are taken out when the share ends (or after four segments);
+//   * a segment that covers a tile's whole K range goes through shared memory straight to the epilogue.  Otherwise
+//     the raw partial tile goes to a scratch slot in global memory, and once every CTA that holds a part of the tile
+//     has handed its part in, each of them adds up - IN SLOT (= K) ORDER, whoever does it - and finishes its own
+//     slice of the tile's activation rows: one round trip of loads per CTA, results that do not depend on timing;
 //   * between phases a grid-wide barrier (sense reversing, in global memory); a CTA's weight producers do not wait
 //     for it - the next phase's weights are already on their way into registers and tensor memory while the barrier
 //     is pending; only the activation loads (TMA) of the next phase do;
@@ -25,6 +29,8 @@
 // Replaces math::matmat_i8_weight_parallel + transpose_rb_to_br (reference src/math.rs:223-290) for the batched
 // decode step, with math::rms_norm (src/math.rs:4-22), the rotary embedding and KV write (src/model.rs:1065-1107),
 // SwiGLU and the residual adds (src/model.rs:1127-1167) folded into the epilogues.
+#include <stdlib.h>
+
 #include <algorithm>
 #include <new>
 
@@ -36,13 +42,39 @@ using namespace pi_tc;
 constexpr int kMaxPhases = 4;
 constexpr uint32_t kGridSpinLimit = 1u << 22;   // polls, 32 ns apart
 
+// Optional per-CTA timeline (compile with -DPI_CHAIN_TRACE): %globaltimer stamps of the steps of every phase, written
+// to a buffer that the launcher dumps to the file named by the environment variable PI_CHAIN_TRACE_FILE.
+#ifdef PI_CHAIN_TRACE
+#define PI_TRACE(cp, cta, slot)                                                             \
+  do {                                                                                      \
+    unsigned long long _t;                                                                  \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t));                                  \
+    (cp).trace[(size_t)(cta) * 64 + (slot)] = _t;                                           \
+  } while (0)
+#define PI_TRACE_FIRST(cp, cta, slot)     /* once per phase: `trace_seen` is a local bit mask of phases */ \
+  do {                                                                                      \
+    const int _ph = ((slot) - 8) / 12;                                                      \
+    if (!(trace_seen & (1u << _ph))) {                                                      \
+      trace_seen |= 1u << _ph;                                                              \
+      PI_TRACE(cp, cta, slot);                                                              \
+    }                                                                                       \
+  } while (0)
+#else
+#define PI_TRACE(cp, cta, slot) do { } while (0)
+#define PI_TRACE_FIRST(cp, cta, slot) do { } while (0)
+#endif
+
 struct ChainParams {
+#ifdef PI_CHAIN_TRACE
+  unsigned long long* trace;  // [grid][64]
+#endif
   GemmParams ph[kMaxPhases];
   int rtiles[kMaxPhases];
   int active[kMaxPhases];     // CTAs that own units of the phase: min(grid, units)
   int nphases;
   float* partials;            // [slots][BN][128] raw partial tiles
   unsigned int* tickets;      // [row tiles] partials handed in; zero between uses
+  unsigned int* done;         // [row tiles] holders of a part that have finished their slice; zero between uses
   unsigned int* bar_count;    // grid barrier: arrivals of the pending generation
   unsigned int* bar_gen;      // generations completed since the buffer was cleared
   int* err_flag;
@@ -122,11 +154,10 @@ __device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, con
   return false;
 }
 
-// What the epilogue of a segment needs from its CTA.
+// What the epilogues need from their CTA.
 struct EpiCtx {
   float* my_part;            // [BN][128] shared
   float* s_rowf;             // [BN] shared
-  int* s_last;               // shared
   volatile int* s_abort;
   volatile int* s_dep_ok;
   uint32_t accum_full, accum_empty;   // mbarriers
@@ -134,28 +165,45 @@ struct EpiCtx {
   int cta;
 };
 
-// The segment of row tile `tile` of phase `ph` that this CTA has just fed to the tensor pipe (`whole`: it covered the
-// tile's entire K range).  All 16 producer warps call this in lock step (it synchronises them with named barrier 1):
-// take the accumulator out of tensor memory as soon as the MMAs are done and release it for the next segment; a whole
-// tile goes through shared memory straight to the epilogue; a partial one goes to its scratch slot in global memory
-// and the CTA that hands in the last partial of the tile adds them in slot (= K) order and runs the epilogue.
-// Out of line on purpose: it runs once per segment and would otherwise be cloned into every slot of the unrolled
-// producer loop.
+constexpr int kMaxSegs = 4;   // accumulators a CTA keeps in tensor memory before it must take them out
+
+// A run of segments whose accumulators are waiting in tensor memory: consecutive row tiles t0 .. t0 + nseg - 1 of one
+// phase; the first starts at K block kb0, the last ends with K block kb_last, the ones between cover all of K.
+struct SegBatch {
+  int ph, t0, nseg, kb0, kb_last;
+};
+
+__device__ __forceinline__ bool seg_whole(const SegBatch& b, int j, int nkb) {
+  return (j > 0 || b.kb0 == 0) && (j < b.nseg - 1 || b.kb_last == nkb - 1);
+}
+
+// Which CTAs hold a part of row tile `tile`: [first, first + n).
+__device__ __forceinline__ void tile_holders(const ChainParams& cp, int ph, int tile, int* first, int* n) {
+  const int nkb = cp.ph[ph].nkb;
+  const long U = (long)cp.rtiles[ph] * nkb;
+  const int act = cp.active[ph];
+  const int c0 = owner_of((long)tile * nkb, U, act), c1 = owner_of((long)(tile + 1) * nkb - 1, U, act);
+  *first = c0;
+  *n = c1 - c0 + 1;
+}
+
+// Take the accumulators of a batch of segments out of tensor memory.  All 16 producer warps call this in lock step
+// (named barrier 1).  Partial tiles go to their scratch slots first and are handed in at once (a ticket per tile), so
+// that the other holders of those tiles are not kept waiting; whole tiles then go through shared memory, one after
+// the other, to their epilogue.  Out of line on purpose: it would otherwise be cloned into every slot of the
+// unrolled producer loop.
 template <int BN>
-__device__ __noinline__ void segment_epilogue(const ChainParams& cp, const EpiCtx& e, int ph, int tile, bool whole, int sg) {
+__device__ __noinline__ void batch_drain(const ChainParams& cp, const EpiCtx& e, SegBatch b, int batch_no) {
   constexpr int kTileFloats = BN * kBM;
+  constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int quad = warp & 3, half = (warp >> 2) & 1;
-  const GemmParams& p = cp.ph[ph];
-  const long U = (long)cp.rtiles[ph] * p.nkb;
-  const int act = cp.active[ph];
-  const int c_first = owner_of((long)tile * p.nkb, U, act), c_last = owner_of((long)(tile + 1) * p.nkb - 1, U, act);
-  float* my_part = e.my_part;
-  float* part_dst = whole ? my_part : cp.partials + (size_t)(e.cta + tile) * kTileFloats;
+  const GemmParams& p = cp.ph[b.ph];
+  const bool drainer = warp < kParkWarps && (BN >= 32 || half == 0);
+  int got = 0;
   if (warp < kParkWarps) {
-    int got = 0;
     if (lane == 0) {
-      got = (!*e.s_abort && mbar_wait_dep(e.accum_full, (uint32_t)(sg & 1), e.s_dep_ok)) ? 1 : 0;
+      got = (!*e.s_abort && mbar_wait_dep(e.accum_full, (uint32_t)(batch_no & 1), e.s_dep_ok)) ? 1 : 0;
       if (!got && !*e.s_abort) {
         *e.s_abort = 1;
         if (cp.err_flag) atomicExch(cp.err_flag, 5);
@@ -163,64 +211,121 @@ __device__ __noinline__ void segment_epilogue(const ChainParams& cp, const EpiCt
     }
     got = __shfl_sync(0xffffffffu, got, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    constexpr int kColsPerHalf = BN / 2 >= 16 ? BN / 2 : 16;  // BN 16: only the first half works
-    if (BN >= 32 || half == 0) {
-      const uint32_t my_d = e.tmem_d + ((uint32_t)(quad * 32) << 16);
+    // The accumulate is over, so the phase before this one is complete: the row factors (1/rms from the sums of
+    // squares that phase emitted) can be read now.  Their readers come after the next named barrier.
+    if (tid < BN) e.s_rowf[tid] = act_row_factor(p, tid);
+  }
+  // accumulator of segment j (BN columns from column j * BN) -> dst[c][128 rows]
+  auto drain = [&](int j, float* dst) {
+    const uint32_t my_d = e.tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(j * BN);
 #pragma unroll 1
-      for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
-        float v[16];
-        if (got) {
-          tmem_ld_sum16<BN>(my_d, c0, v);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) part_dst[(c0 + j) * kBM + quad * 32 + lane] = v[j];
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(e.accum_empty);   // the next segment's MMAs may overwrite the accumulator
-    }
-    if (!whole) __threadfence();
-  }
-  if (tid < BN) e.s_rowf[tid] = act_row_factor(p, tid);
-  EpiRows rows;
-  epi_rows_load(p, tile * kBM, tid, rows);
-  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-  bool finish = true;
-  if (!whole) {   // hand the partial in; whoever hands in the last one of the tile finishes it
-    if (tid == 0) {
-      const unsigned int n = (unsigned int)(c_last - c_first + 1);
-      const unsigned int t = atom_add_acq_rel(cp.tickets + tile, 1u);
-      *e.s_last = (t == n - 1u) ? 1 : 0;
-      if (t == n - 1u) cp.tickets[tile] = 0u;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-    finish = *e.s_last != 0;
-    if (finish) __threadfence();
-  }
-  if (finish) {
-    const int r4 = lane * 4, csub = warp;   // 16 activation rows in flight per pass
-    const int nparts = c_last - c_first + 1;
-    const float* slot0 = cp.partials + (size_t)(c_first + tile) * kTileFloats + r4;
-    for (int c = csub; c < BN; c += kProducerWarps) {
-      float4 acc;
-      if (whole) {
-        acc = *reinterpret_cast<const float4*>(my_part + c * kBM + r4);
+    for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
+      uint32_t r[16];
+      if (got) {
+        tmem_ld16_issue(my_d + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       } else {
-        acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int j = 0; j < nparts; ++j) {   // slot order = K order: the same sum whoever adds it up
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0u;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dst[(c0 + i) * kBM + quad * 32 + lane] = __uint_as_float(r[i]);
+    }
+  };
+  // 1. partial tiles: scratch slot (cta + tile), then one ticket per tile
+  bool any_partial = false;
+  for (int j = 0; j < b.nseg; ++j) {
+    if (seg_whole(b, j, p.nkb)) continue;
+    any_partial = true;
+    if (drainer) drain(j, cp.partials + (size_t)(e.cta + b.t0 + j) * kTileFloats);
+  }
+  if (any_partial) {
+    if (drainer) __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+    if (tid == 0)
+      for (int j = 0; j < b.nseg; ++j)
+        if (!seg_whole(b, j, p.nkb)) atom_add_acq_rel(cp.tickets + b.t0 + j, 1u);
+    if (tid == 0) PI_TRACE(cp, e.cta, 8 + b.ph * 12 + 6);
+  }
+  if (!any_partial) asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // s_rowf is written
+  // 2. whole tiles: through shared memory to the epilogue
+  for (int j = 0; j < b.nseg; ++j) {
+    if (!seg_whole(b, j, p.nkb)) continue;
+    const int tile = b.t0 + j;
+    if (drainer) drain(j, e.my_part);
+    EpiRows rows;
+    epi_rows_load(p, tile * kBM, tid, rows);
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+    for (int c = warp; c < BN; c += kProducerWarps)
+      epi_row(p, rows, tile, c, e.s_rowf[c], *reinterpret_cast<const float4*>(e.my_part + c * kBM + lane * 4), lane);
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // my_part is free again
+  }
+  // 3. every accumulator of the batch has been read: the tensor pipe may overwrite them
+  if (drainer) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(e.accum_empty);
+  }
+}
+
+// The end of this CTA's share of a phase: the row tiles it holds only a part of (its first and/or its last) are finished
+// together with the other holders.  Each holder waits until all parts of the tile are handed in (bounded), then adds
+// up and finishes the activation rows c = its index among the holders, + their number, ...; the sum runs over the
+// slots in K order, so it is the same whoever computes it.  The last holder to finish clears the tile's counters.
+template <int BN>
+__device__ __noinline__ void share_finish(const ChainParams& cp, const EpiCtx& e, int ph, int tile_a, int tile_b) {
+  constexpr int kTileFloats = BN * kBM;
+  __shared__ int s_ok;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const GemmParams& p = cp.ph[ph];
+  for (int k = 0; k < 2; ++k) {
+    const int tile = k == 0 ? tile_a : tile_b;
+    if (tile < 0) continue;
+    int first, n;
+    tile_holders(cp, ph, tile, &first, &n);
+    if (tid == 0) {
+      int ok = 0;
+      for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+        if (ld_acquire_u32(cp.tickets + tile) >= (unsigned int)n) {
+          ok = 1;
+          break;
+        }
+        if (*e.s_abort) break;
+        __nanosleep(20);
+      }
+      if (!ok && !*e.s_abort) {
+        *e.s_abort = 1;
+        if (cp.err_flag) atomicExch(cp.err_flag, 8);
+      }
+      s_ok = ok;
+      PI_TRACE(cp, e.cta, 8 + ph * 12 + 7);
+    }
+    EpiRows rows;
+    epi_rows_load(p, tile * kBM, tid, rows);
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+    if (s_ok) {
+      __threadfence();
+      const int mine = e.cta - first;
+      const float* slot0 = cp.partials + (size_t)(first + tile) * kTileFloats + lane * 4;
+      for (int c = mine + warp * n; c < BN; c += kProducerWarps * n) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int j = 0; j < n; ++j) {   // slot order = K order
           const float4 v = __ldcg(reinterpret_cast<const float4*>(slot0 + (size_t)j * kTileFloats + c * kBM));
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
+        epi_row(p, rows, tile, c, e.s_rowf[c], acc, lane);
       }
-      epi_row(p, rows, tile, c, e.s_rowf[c], acc, lane);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+    if (tid == 0) {   // all holders have read every part before the counters (and, a phase later, the slots) are reused
+      const unsigned int d = atom_add_acq_rel(cp.done + tile, 1u);
+      if (d == (unsigned int)n - 1u) {
+        cp.tickets[tile] = 0u;
+        cp.done[tile] = 0u;
+      }
     }
   }
-  asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
-  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // stores issued, my_part and s_rowf free
 }
 
 template <int BN, int STAGES>
@@ -228,13 +333,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant__ ChainMaps maps) {
   constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
   constexpr int kBStageBytes = 2 * kBAtomBytes;
-  constexpr int kDCols = kPlanes * BN;
+  constexpr int kPlaneBytes = BN * 128;                      // one plane of an atom
+  constexpr int kDCols = kMaxSegs * BN;                      // accumulators of up to four segments
   constexpr int kAStart = (kDCols + 63) / 64 * 64;          // weight stages start on a 64-column boundary
-  static_assert(kDCols <= 256, "one MMA covers at most 256 accumulator columns");
   static_assert(kAStart + STAGES * kACols <= 512, "TMEM holds 512 columns");
   constexpr int kTmemCols = 512;
-  constexpr int kEpiWarps = BN >= 32 ? kParkWarps : 4;      // warps that move the accumulator out of TMEM
-  constexpr int kTileFloats = BN * kBM;
+  constexpr int kEpiWarps = BN >= 32 ? kParkWarps : 4;      // warps that move the accumulators out of TMEM
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long bars[2 * STAGES + 2];
@@ -242,18 +346,21 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   __shared__ volatile unsigned int s_base_gen;   // barrier generations completed before this launch began
   __shared__ volatile int s_abort;
   __shared__ volatile int s_dep_ok;   // the preceding kernel has completed and s_base_gen is recorded
-  __shared__ int s_last;           // this CTA handed in the last partial of the tile
-  __shared__ float s_rowf[BN];     // row factor of the activation rows
+  __shared__ float s_rowf[BN];        // row factor of the activation rows
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int quad = warp & 3, kq = (warp >> 2) & 3, half = (warp >> 2) & 1;
+  const int quad = warp & 3, kq = (warp >> 2) & 3;
   const int cta = blockIdx.x, G = gridDim.x;
+#ifdef PI_CHAIN_TRACE
+  unsigned int trace_seen = 0;
+#endif
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
   const uint32_t accum_full = smem_u32(&bars[2 * STAGES]), accum_empty = smem_u32(&bars[2 * STAGES + 1]);
   float* my_part = reinterpret_cast<float*>(smem + STAGES * kBStageBytes);   // [BN][128], apart from the B stages
   pi_grid_launch_dependents();
+  if (tid == 0) PI_TRACE(cp, cta, 0);
 
-  // ---- weight producers: the first group of loads goes out before anything else (weights depend on nothing) ----
+  // ---- weight producers: the first loads go out before anything else (weights depend on nothing) ----------------
   // Rolling prefetch: the 32 bytes of unit i + 4 are requested into the register slot that unit i has just left.
   constexpr int kGroup = 4;
   uint32_t cur[kGroup][8];
@@ -313,12 +420,12 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   };
 
   if (warp < kProducerWarps) {
-    // ================= weight producers + epilogue =================================================================
+    // ================= weight producers + epilogues ================================================================
     UnitIter cu;
     cu.ph = 0;
     iter_enter(cu, cp, cta);
     bool dep_waited = false;
-    int it = 0, sg = 0, seg_kb0 = 0;
+    int it = 0, batch_no = 0;
     int arrived = 0;   // grid barriers this CTA has arrived at (thread 0 only)
     // Arrive at the barriers that end phases [arrived, upto): thread 0, after every thread's stores of the phase.
     auto arrive_upto = [&](int upto) {
@@ -344,13 +451,15 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
     EpiCtx ec;
     ec.my_part = my_part;
     ec.s_rowf = s_rowf;
-    ec.s_last = &s_last;
     ec.s_abort = &s_abort;
     ec.s_dep_ok = &s_dep_ok;
     ec.accum_full = accum_full;
     ec.accum_empty = accum_empty;
     ec.tmem_d = tmem;
     ec.cta = cta;
+    SegBatch batch;     // segments whose accumulators are waiting in tensor memory
+    batch.nseg = 0;
+    int share_ph = -1, share_t0 = 0, share_kb0 = 0;   // where this CTA's share of the current phase began
     // Once a wait has run out (s_abort) the warps stop waiting and stop feeding the pipeline, but they still walk
     // their units to the end: the named barriers of the epilogues below must be reached by all 16 warps in lock step.
     while (cu.ph < cp.nphases) {
@@ -358,12 +467,23 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
       for (int d = 0; d < kGroup; ++d) {
         if (cu.ph >= cp.nphases) break;
         const int s = it % STAGES;
-        if (cu.first) seg_kb0 = cu.kb;
+        if (cu.ph != share_ph) {   // first unit of this CTA's share of a phase
+          share_ph = cu.ph;
+          share_t0 = cu.tile;
+          share_kb0 = cu.kb;
+        }
+        if (cu.first && batch.nseg == 0) {
+          batch.ph = cu.ph;
+          batch.t0 = cu.tile;
+          batch.kb0 = cu.kb;
+        }
         uint32_t h[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
         if (pf.ph < cp.nphases) {
+#ifndef PI_CHAIN_DBG_NO_W
           ld_stream_32(unit_ptr(pf), &cur[d][0]);
+#endif
           iter_next(pf, cp, cta);
         }
         int ok = 1;
@@ -376,6 +496,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(full0 + 8 * s);
+          if (tid == 0) PI_TRACE_FIRST(cp, cta, 8 + cu.ph * 12 + 4);
         } else if (lane == 0 && !s_abort) {
           s_abort = 1;
           if (cp.err_flag) atomicExch(cp.err_flag, 2);
@@ -383,17 +504,34 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
         ++it;
 
         if (iter_seg_last(cu)) {
-          // ---- the segment [seg_kb0, cu.kb] of row tile cu.tile is in flight: take its accumulator and finish it ----
-          if (!dep_waited) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");   // the epilogue reads what the preceding kernel wrote
-            dep_waited = true;
-          }
-          segment_epilogue<BN>(cp, ec, cu.ph, cu.tile, seg_kb0 == 0 && cu.kb == cu.nkb - 1, sg);
-          ++sg;
-          if (cu.left == 1 && tid == 0) {   // that was this CTA's last segment of the phase
-            UnitIter nx = cu;
-            iter_next(nx, cp, cta);
-            arrive_upto(nx.ph);
+          ++batch.nseg;
+          batch.kb_last = cu.kb;
+          const bool share_end = cu.left == 1;
+          if (share_end || batch.nseg == kMaxSegs) {
+            // ---- take the pending accumulators out; at the end of the share also finish the split tiles ------------
+            if (!dep_waited) {
+              asm volatile("griddepcontrol.wait;" ::: "memory");   // the epilogues read what the preceding kernel wrote
+              dep_waited = true;
+            }
+            if (tid == 0) PI_TRACE(cp, cta, 8 + cu.ph * 12 + 5);
+            batch_drain<BN>(cp, ec, batch, batch_no);
+            ++batch_no;
+            batch.nseg = 0;
+            if (share_end) {
+              const int nkb = cu.nkb;
+              const int tile_a = share_kb0 != 0 ? share_t0 : ((cu.tile == share_t0 && cu.kb != nkb - 1) ? share_t0 : -1);
+              const int tile_b = (cu.kb != nkb - 1 && cu.tile != share_t0) ? cu.tile : -1;
+              if (tile_a >= 0 || tile_b >= 0) share_finish<BN>(cp, ec, cu.ph, tile_a, tile_b);
+              asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
+              asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // every thread's stores are issued
+              if (tid == 0) {
+                PI_TRACE(cp, cta, 8 + cu.ph * 12 + 8);
+                UnitIter nx = cu;
+                iter_next(nx, cp, cta);
+                arrive_upto(nx.ph);
+                PI_TRACE(cp, cta, 8 + cu.ph * 12 + 9);
+              }
+            }
           }
         }
         iter_next(cu, cp, cta);
@@ -412,6 +550,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
       s_base_gen = ld_acquire_u32(cp.bar_gen);
       __threadfence_block();
       s_dep_ok = 1;
+      PI_TRACE(cp, cta, 1);
       while (cu.ph < cp.nphases) {
         if (cu.ph != ready_ph) {
           if (cu.ph > 0) {
@@ -423,6 +562,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
             asm volatile("fence.proxy.async.global;" ::: "memory");
           }
           ready_ph = cu.ph;
+          PI_TRACE(cp, cta, 8 + cu.ph * 12 + 0);
         }
         const int s = it % STAGES;
         if (s_abort) break;
@@ -433,7 +573,12 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
         }
         const uint32_t bar = full0 + 8 * s;
         const uint32_t b_stage = smem_base + s * kBStageBytes;
+#ifdef PI_CHAIN_DBG_NO_B
+        mbar_arrive(bar);
+        if (false)
+#else
         mbar_arrive_expect_tx(bar, kBStageBytes);
+#endif
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
           asm volatile(
@@ -443,6 +588,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
               : "memory");
         }
         issued = true;
+        PI_TRACE_FIRST(cp, cta, 8 + cu.ph * 12 + 1);
         ++it;
         iter_next(cu, cp, cta);
       }
@@ -452,16 +598,17 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   } else {
     // ================= MMA issuer ==================================================================================
     if (lane == 0) {
-      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = bf16, N = 3*BN, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kDCols >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = bf16, M = 128, N = BN: the three planes of a K step are
+      // three MMAs into the same accumulator columns
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       UnitIter cu;
       cu.ph = 0;
       iter_enter(cu, cp, cta);
-      int it = 0, sg = 0;
+      int it = 0, nseg = 0, batch_no = 0;
       while (cu.ph < cp.nphases) {
         const int s = it % STAGES;
-        if (cu.first && sg > 0) {   // the epilogue of the previous segment has emptied the accumulator
-          if (s_abort || !mbar_wait_dep(accum_empty, (uint32_t)((sg - 1) & 1), &s_dep_ok)) {
+        if (cu.first && nseg == 0 && batch_no > 0) {   // the accumulators of the previous batch have been taken out
+          if (s_abort || !mbar_wait_dep(accum_empty, (uint32_t)((batch_no - 1) & 1), &s_dep_ok)) {
             if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 7);
             s_abort = 1;
             break;
@@ -473,20 +620,30 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t db0 = smem_desc(smem_base + s * kBStageBytes);
+        PI_TRACE_FIRST(cp, cta, 8 + cu.ph * 12 + 2);
+        const uint32_t stage_addr = smem_base + s * kBStageBytes;
         const uint32_t a_s = tmem_a0 + (uint32_t)(s * kACols);
+        const uint32_t d_seg = tmem + (uint32_t)(nseg * BN);
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {  // 16 K elements: 8 TMEM columns of A, 32 bytes of every B row
-            const uint64_t db = db0 + (uint64_t)((atom * kBAtomBytes + ks * 32) >> 4);
-            umma_f16_ts(tmem, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (!cu.first || atom + ks > 0) ? 1u : 0u);
+#pragma unroll
+            for (int pl = 0; pl < kPlanes; ++pl) {
+              const uint64_t db = smem_desc(stage_addr + atom * kBAtomBytes + pl * kPlaneBytes) + (uint64_t)((ks * 32) >> 4);
+              umma_f16_ts(d_seg, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (!cu.first || atom + ks + pl > 0) ? 1u : 0u);
+            }
           }
         }
         umma_commit(empty0 + 8 * s);  // the stage (TMEM columns and shared tile) is free once these MMAs are done
         if (iter_seg_last(cu)) {
-          umma_commit(accum_full);
-          ++sg;
+          ++nseg;
+          if (cu.left == 1 || nseg == kMaxSegs) {
+            umma_commit(accum_full);
+            PI_TRACE(cp, cta, 8 + cu.ph * 12 + 3);
+            nseg = 0;
+            ++batch_no;
+          }
         }
         ++it;
         iter_next(cu, cp, cta);
@@ -583,7 +740,7 @@ pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
     q->ws_slots = std::max(slots, q->ws_slots);
     q->ws_tiles = std::max(tiles, q->ws_tiles);
     q->ws_bn = std::max(BN, q->ws_bn);
-    const size_t bytes = q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float) + (q->ws_tiles + 64) * sizeof(unsigned int);
+    const size_t bytes = q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float) + (2 * q->ws_tiles + 64) * sizeof(unsigned int);
     PI_CUDA(ctx, cudaMalloc(&q->ws, bytes));
     PI_CUDA(ctx, cudaMemsetAsync(q->ws, 0, bytes, ctx->stream));
   }
@@ -592,6 +749,14 @@ pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
   q->cp.bar_count = words;          // a 128-byte line of its own
   q->cp.bar_gen = words + 32;
   q->cp.tickets = words + 64;
+  q->cp.done = words + 64 + q->ws_tiles;
+#ifdef PI_CHAIN_TRACE
+  static unsigned long long* trace_dev = nullptr;
+  const size_t trace_bytes = (size_t)256 * 64 * sizeof(unsigned long long);
+  if (!trace_dev) cudaMalloc(&trace_dev, trace_bytes);
+  cudaMemsetAsync(trace_dev, 0, trace_bytes, ctx->stream);
+  q->cp.trace = trace_dev;
+#endif
   cudaError_t err;
   switch (BN) {
     case 16: err = launch_chain<16, 6>(ctx, *q, grid); break;
@@ -600,6 +765,23 @@ pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
   }
   if (err != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "projection chain launch (%d phases) failed: %s", n, cudaGetErrorString(err));
   ctx->launches++;
+#ifdef PI_CHAIN_TRACE
+  if (const char* path = getenv("PI_CHAIN_TRACE_FILE")) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(ctx->stream, &cap);
+    if (cap == cudaStreamCaptureStatusNone) {
+      std::vector<unsigned long long> host((size_t)256 * 64);
+      cudaStreamSynchronize(ctx->stream);
+      cudaMemcpy(host.data(), trace_dev, trace_bytes, cudaMemcpyDeviceToHost);
+      if (FILE* f = fopen(path, "ab")) {
+        const int hdr[4] = {n, grid, BN, 0};
+        fwrite(hdr, sizeof(int), 4, f);
+        fwrite(host.data(), sizeof(unsigned long long), host.size(), f);
+        fclose(f);
+      }
+    }
+  }
+#endif
   return PI_OK;
 }
 
@@ -614,7 +796,7 @@ void pi_gemm_chain_reset_sync(pi_ctx* ctx) {
   ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
   if (!q || !q->ws) return;
   unsigned char* words = static_cast<unsigned char*>(q->ws) + q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float);
-  cudaMemsetAsync(words, 0, (q->ws_tiles + 64) * sizeof(unsigned int), ctx->stream);
+  cudaMemsetAsync(words, 0, (2 * q->ws_tiles + 64) * sizeof(unsigned int), ctx->stream);
 }
 
 void pi_gemm_chain_destroy(pi_ctx* ctx) {
