@@ -8,15 +8,15 @@
 //
 //   * every phase's work is its (row tile, K block) units in row-tile-major order, cut into equal contiguous shares,
 //     one per CTA - a wide matrix ([gate;up]: 88 row tiles) and a narrow one (o, down: 16) both keep all SMs busy;
-//   * a CTA's share is a few "segments" (a K range of one row tile).  Each segment has an accumulator of its own in
-//     tensor memory (the three bf16 planes of the activations accumulate into the SAME columns, so a segment needs
-//     only as many columns as there are activation rows), so the tensor pipe runs through the whole share without
-//     waiting for an epilogue; the accumulators are taken out when the share ends (or after four segments);
+//   * a CTA's share is a few "segments" (a K range of one row tile).  Tensor memory holds the accumulators of two
+//     segments, so the tensor pipe runs through a share that crosses a tile boundary without waiting for an
+//     epilogue; the accumulators are taken out when the share ends (or after two segments);
 //   * a segment that covers a tile's whole K range goes through shared memory straight to the epilogue.  Otherwise
 //     the raw partial tile goes to a scratch slot in global memory, and once every CTA that holds a part of the tile
 //     has handed its part in, each of them adds up - IN SLOT (= K) ORDER, whoever does it - and finishes its own
 //     slice of the tile's activation rows: one round trip of loads per CTA, results that do not depend on timing;
-//   * between phases a grid-wide barrier (sense reversing, in global memory); a CTA's weight producers do not wait
+//   * between phases a grid-wide barrier (a counter in global memory that only grows: arriving is one fire-and-forget
+//     reduction, waiting is polling for this launch's target); a CTA's weight producers do not wait
 //     for it - the next phase's weights are already on their way into registers and tensor memory while the barrier
 //     is pending; only the activation loads (TMA) of the next phase do;
 //   * TMEM, the mbarriers and the pipeline state are set up once.
@@ -73,10 +73,10 @@ struct ChainParams {
   int active[kMaxPhases];     // CTAs that own units of the phase: min(grid, units)
   int nphases;
   float* partials;            // [slots][BN][128] raw partial tiles
-  unsigned int* tickets;      // [row tiles] partials handed in; zero between uses
-  unsigned int* done;         // [row tiles] holders of a part that have finished their slice; zero between uses
-  unsigned int* bar_count;    // grid barrier: arrivals of the pending generation
-  unsigned int* bar_gen;      // generations completed since the buffer was cleared
+  unsigned int* tickets;      // [2][max_tiles] parts handed in per row tile; zero between uses; phase ph uses half ph & 1
+  unsigned int* done;         // [2][max_tiles] holders of a part that have finished their slice; zero between uses
+  int max_tiles;
+  unsigned int* bar_count;    // [phases] x 32 words: arrivals at the barrier after each phase since the buffer was cleared
   int* err_flag;
 };
 struct ChainMaps {
@@ -132,10 +132,10 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
   return v;
 }
 
-__device__ __forceinline__ unsigned int atom_add_acq_rel(unsigned int* p, unsigned int v) {
-  unsigned int old;
-  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-  return old;
+// Fire-and-forget arrival: orders this thread's earlier writes (and, after a CTA barrier and a fence, its CTA's) before
+// the increment becomes visible; nothing comes back, so the thread does not wait for the round trip.
+__device__ __forceinline__ void red_add_release(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Bounded wait on an mbarrier; polls are only counted once the grid dependency of this launch is resolved (until
@@ -165,7 +165,7 @@ struct EpiCtx {
   int cta;
 };
 
-constexpr int kMaxSegs = 4;   // accumulators a CTA keeps in tensor memory before it must take them out
+constexpr int kMaxSegs = 2;   // segment accumulators (three column groups each) that tensor memory holds
 
 // A run of segments whose accumulators are waiting in tensor memory: consecutive row tiles t0 .. t0 + nseg - 1 of one
 // phase; the first starts at K block kb0, the last ends with K block kb_last, the ones between cover all of K.
@@ -188,10 +188,10 @@ __device__ __forceinline__ void tile_holders(const ChainParams& cp, int ph, int 
 }
 
 // Take the accumulators of a batch of segments out of tensor memory.  All 16 producer warps call this in lock step
-// (named barrier 1).  Partial tiles go to their scratch slots first and are handed in at once (a ticket per tile), so
-// that the other holders of those tiles are not kept waiting; whole tiles then go through shared memory, one after
-// the other, to their epilogue.  Out of line on purpose: it would otherwise be cloned into every slot of the
-// unrolled producer loop.
+// (named barrier 1).  Partial tiles go to their scratch slots first and are handed in at once (a ticket per tile,
+// fire and forget), so that the other holders of those tiles are not kept waiting; whole tiles then go through shared
+// memory, one after the other, to their epilogue.  Out of line on purpose: it would otherwise be cloned into every
+// slot of the unrolled producer loop.
 template <int BN>
 __device__ __noinline__ void batch_drain(const ChainParams& cp, const EpiCtx& e, SegBatch b, int batch_no) {
   constexpr int kTileFloats = BN * kBM;
@@ -215,21 +215,20 @@ __device__ __noinline__ void batch_drain(const ChainParams& cp, const EpiCtx& e,
     // squares that phase emitted) can be read now.  Their readers come after the next named barrier.
     if (tid < BN) e.s_rowf[tid] = act_row_factor(p, tid);
   }
-  // accumulator of segment j (BN columns from column j * BN) -> dst[c][128 rows]
+  // accumulator of segment j (three groups of BN columns from column j * 3 * BN, added) -> dst[c][128 rows]
   auto drain = [&](int j, float* dst) {
-    const uint32_t my_d = e.tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(j * BN);
+    const uint32_t my_d = e.tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(j * kPlanes * BN);
 #pragma unroll 1
     for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
-      uint32_t r[16];
+      float v[16];
       if (got) {
-        tmem_ld16_issue(my_d + (uint32_t)c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tmem_ld_sum16<BN>(my_d, c0, v);
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = 0u;
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) dst[(c0 + i) * kBM + quad * 32 + lane] = __uint_as_float(r[i]);
+      for (int i = 0; i < 16; ++i) dst[(c0 + i) * kBM + quad * 32 + lane] = v[i];
     }
   };
   // 1. partial tiles: scratch slot (cta + tile), then one ticket per tile
@@ -239,15 +238,14 @@ __device__ __noinline__ void batch_drain(const ChainParams& cp, const EpiCtx& e,
     any_partial = true;
     if (drainer) drain(j, cp.partials + (size_t)(e.cta + b.t0 + j) * kTileFloats);
   }
-  if (any_partial) {
-    if (drainer) __threadfence();
-    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-    if (tid == 0)
-      for (int j = 0; j < b.nseg; ++j)
-        if (!seg_whole(b, j, p.nkb)) atom_add_acq_rel(cp.tickets + b.t0 + j, 1u);
-    if (tid == 0) PI_TRACE(cp, e.cta, 8 + b.ph * 12 + 6);
+  if (any_partial && drainer) __threadfence();
+  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // parts are out, s_rowf is written
+  if (any_partial && tid == 0) {
+    unsigned int* tk = cp.tickets + (size_t)(b.ph & 1) * cp.max_tiles;
+    for (int j = 0; j < b.nseg; ++j)
+      if (!seg_whole(b, j, p.nkb)) red_add_release(tk + b.t0 + j, 1u);
+    PI_TRACE(cp, e.cta, 8 + b.ph * 12 + 6);
   }
-  if (!any_partial) asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");   // s_rowf is written
   // 2. whole tiles: through shared memory to the epilogue
   for (int j = 0; j < b.nseg; ++j) {
     if (!seg_whole(b, j, p.nkb)) continue;
@@ -271,81 +269,95 @@ __device__ __noinline__ void batch_drain(const ChainParams& cp, const EpiCtx& e,
 // The end of this CTA's share of a phase: the row tiles it holds only a part of (its first and/or its last) are finished
 // together with the other holders.  Each holder waits until all parts of the tile are handed in (bounded), then adds
 // up and finishes the activation rows c = its index among the holders, + their number, ...; the sum runs over the
-// slots in K order, so it is the same whoever computes it.  The last holder to finish clears the tile's counters.
+// slots in K order, so it is the same whoever computes it.  The last holder to finish clears the tile's counters
+// (their half of the counter arrays is not used again before the phase after the next).
 template <int BN>
 __device__ __noinline__ void share_finish(const ChainParams& cp, const EpiCtx& e, int ph, int tile_a, int tile_b) {
   constexpr int kTileFloats = BN * kBM;
   __shared__ int s_ok;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const GemmParams& p = cp.ph[ph];
-  for (int k = 0; k < 2; ++k) {
-    const int tile = k == 0 ? tile_a : tile_b;
-    if (tile < 0) continue;
-    int first, n;
-    tile_holders(cp, ph, tile, &first, &n);
-    if (tid == 0) {
-      int ok = 0;
-      for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
-        if (ld_acquire_u32(cp.tickets + tile) >= (unsigned int)n) {
-          ok = 1;
-          break;
-        }
-        if (*e.s_abort) break;
-        __nanosleep(20);
+  unsigned int* tk = cp.tickets + (size_t)(ph & 1) * cp.max_tiles;
+  unsigned int* dn = cp.done + (size_t)(ph & 1) * cp.max_tiles;
+  int first[2] = {0, 0}, n[2] = {0, 0};
+  const int tiles[2] = {tile_a, tile_b};
+  for (int k = 0; k < 2; ++k)
+    if (tiles[k] >= 0) tile_holders(cp, ph, tiles[k], &first[k], &n[k]);
+  if (tid == 0) {   // both tiles' parts are waited for together
+    int ok = 0;
+    for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
+      const bool a = tiles[0] < 0 || ld_acquire_u32(tk + tiles[0]) >= (unsigned int)n[0];
+      const bool b = tiles[1] < 0 || ld_acquire_u32(tk + tiles[1]) >= (unsigned int)n[1];
+      if (a && b) {
+        ok = 1;
+        break;
       }
-      if (!ok && !*e.s_abort) {
-        *e.s_abort = 1;
-        if (cp.err_flag) atomicExch(cp.err_flag, 8);
-      }
-      s_ok = ok;
-      PI_TRACE(cp, e.cta, 8 + ph * 12 + 7);
+      if (*e.s_abort) break;
+      __nanosleep(20);
     }
-    EpiRows rows;
-    epi_rows_load(p, tile * kBM, tid, rows);
-    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-    if (s_ok) {
-      __threadfence();
-      const int mine = e.cta - first;
-      const float* slot0 = cp.partials + (size_t)(first + tile) * kTileFloats + lane * 4;
-      for (int c = mine + warp * n; c < BN; c += kProducerWarps * n) {
+    if (!ok && !*e.s_abort) {
+      *e.s_abort = 1;
+      if (cp.err_flag) atomicExch(cp.err_flag, 8);
+    }
+    s_ok = ok;
+    PI_TRACE(cp, e.cta, 8 + ph * 12 + 7);
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+  if (s_ok) {
+    __threadfence();
+    for (int k = 0; k < 2; ++k) {
+      const int tile = tiles[k];
+      if (tile < 0) continue;
+      EpiRows rows;
+      epi_rows_load(p, tile * kBM, tid, rows);
+      const int mine = e.cta - first[k], nn = n[k];
+      const float* slot0 = cp.partials + (size_t)(first[k] + tile) * kTileFloats + lane * 4;
+      for (int c = mine + warp * nn; c < BN; c += kProducerWarps * nn) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-        for (int j = 0; j < n; ++j) {   // slot order = K order
+        for (int j = 0; j < nn; ++j) {   // slot order = K order
           const float4 v = __ldcg(reinterpret_cast<const float4*>(slot0 + (size_t)j * kTileFloats + c * kBM));
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         epi_row(p, rows, tile, c, e.s_rowf[c], acc, lane);
       }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
-    if (tid == 0) {   // all holders have read every part before the counters (and, a phase later, the slots) are reused
-      const unsigned int d = atom_add_acq_rel(cp.done + tile, 1u);
-      if (d == (unsigned int)n - 1u) {
-        cp.tickets[tile] = 0u;
-        cp.done[tile] = 0u;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kProducerWarps * 32) : "memory");
+  // Every thread of this CTA has read all parts.  A side thread counts the holders that are through and the last one
+  // clears the counters; nobody waits for that round trip (warp 1 meets it at its next use of the value only).
+  if (tid == 32)
+    for (int k = 0; k < 2; ++k) {
+      if (tiles[k] < 0) continue;
+      unsigned int d;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(d) : "l"(dn + tiles[k]), "r"(1u) : "memory");
+      if (d == (unsigned int)n[k] - 1u) {
+        tk[tiles[k]] = 0u;
+        dn[tiles[k]] = 0u;
       }
     }
-  }
 }
 
-template <int BN, int STAGES>
+template <int BN, int SA, int SB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant__ ChainMaps maps) {
   constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
   constexpr int kBStageBytes = 2 * kBAtomBytes;
-  constexpr int kPlaneBytes = BN * 128;                      // one plane of an atom
-  constexpr int kDCols = kMaxSegs * BN;                      // accumulators of up to four segments
+  constexpr int kSegCols = kPlanes * BN;                     // one segment's accumulator: W*p0 | W*p1 | W*p2
+  constexpr int kDCols = kMaxSegs * kSegCols;
   constexpr int kAStart = (kDCols + 63) / 64 * 64;          // weight stages start on a 64-column boundary
-  static_assert(kAStart + STAGES * kACols <= 512, "TMEM holds 512 columns");
+  static_assert(kSegCols <= 256, "one MMA covers at most 256 accumulator columns");
+  static_assert(kAStart + SA * kACols <= 512, "TMEM holds 512 columns");
   constexpr int kTmemCols = 512;
   constexpr int kEpiWarps = BN >= 32 ? kParkWarps : 4;      // warps that move the accumulators out of TMEM
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 2];
+  // mbarriers: weights in tensor memory (full / empty per A stage), activations in shared memory (per B stage), accumulators
+  __shared__ __align__(8) unsigned long long bars[2 * SA + 2 * SB + 2];
   __shared__ uint32_t s_tmem;
-  __shared__ volatile unsigned int s_base_gen;   // barrier generations completed before this launch began
+  __shared__ volatile unsigned int s_base[kMaxPhases];   // barrier counters before this launch began
   __shared__ volatile int s_abort;
-  __shared__ volatile int s_dep_ok;   // the preceding kernel has completed and s_base_gen is recorded
+  __shared__ volatile int s_dep_ok;   // the preceding kernel has completed and s_base is recorded
   __shared__ float s_rowf[BN];        // row factor of the activation rows
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -354,9 +366,10 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
 #ifdef PI_CHAIN_TRACE
   unsigned int trace_seen = 0;
 #endif
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
-  const uint32_t accum_full = smem_u32(&bars[2 * STAGES]), accum_empty = smem_u32(&bars[2 * STAGES + 1]);
-  float* my_part = reinterpret_cast<float*>(smem + STAGES * kBStageBytes);   // [BN][128], apart from the B stages
+  const uint32_t a_full0 = smem_u32(&bars[0]), a_empty0 = smem_u32(&bars[SA]);
+  const uint32_t b_full0 = smem_u32(&bars[2 * SA]), b_empty0 = smem_u32(&bars[2 * SA + SB]);
+  const uint32_t accum_full = smem_u32(&bars[2 * SA + 2 * SB]), accum_empty = smem_u32(&bars[2 * SA + 2 * SB + 1]);
+  float* my_part = reinterpret_cast<float*>(smem + SB * kBStageBytes);   // [BN][128], apart from the B stages
   pi_grid_launch_dependents();
   if (tid == 0) PI_TRACE(cp, cta, 0);
 
@@ -382,15 +395,18 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   }
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, kProducerWarps + 1);       // one arrival per producer warp + the TMA thread's expect_tx
-      mbar_init(empty0 + 8 * s, 1);                        // one tcgen05.commit
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(a_full0 + 8 * s, kProducerWarps);          // one arrival per producer warp
+      mbar_init(a_empty0 + 8 * s, 1);                      // one tcgen05.commit
+    }
+    for (int s = 0; s < SB; ++s) {
+      mbar_init(b_full0 + 8 * s, 1);                       // the TMA thread's expect_tx
+      mbar_init(b_empty0 + 8 * s, 1);                      // one tcgen05.commit
     }
     mbar_init(accum_full, 1);
     mbar_init(accum_empty, kEpiWarps);
     s_abort = 0;
     s_dep_ok = 0;
-    s_base_gen = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -405,14 +421,17 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   const uint32_t tmem_a0 = tmem + (uint32_t)kAStart;
   const uint32_t smem_base = smem_u32(smem);
 
-  // The barrier words are shared with the preceding launch, which may still be running while this one starts
-  // (programmatic dependent launch).  So the generation count "before this launch" is read only once the preceding
-  // kernel has completed (by the TMA lane, which then raises s_dep_ok), and no thread arrives at a barrier before
-  // that: no barrier of this launch can complete before every CTA has recorded the same base.
-  // Wait until `need` grid barriers of this launch have completed; false when the limit ran out.
+  // The barrier after phase k is a counter that only grows: every CTA adds one when it is through with the phase, and
+  // the barrier is passed once the counter has grown by the size of the grid.  The counters are shared with the
+  // preceding launch, which may still be running while this one starts (programmatic dependent launch).  So their
+  // values "before this launch" are read only once the preceding kernel has completed (by the TMA lane, which then
+  // raises s_dep_ok), and no thread arrives at a barrier before that.
+  // Wait until the first `need` barriers of this launch are passed; false when the limit ran out.
   auto grid_wait = [&](int need) {
+    if (need <= 0) return true;
+    const unsigned int* ctr = cp.bar_count + (size_t)(need - 1) * 32;
     for (uint32_t spin = 0; spin < kGridSpinLimit; ++spin) {
-      if (s_dep_ok && (int)(ld_acquire_u32(cp.bar_gen) - s_base_gen) >= need) return true;
+      if (s_dep_ok && (int)(ld_acquire_u32(ctr) - (s_base[need - 1] + (unsigned int)G)) >= 0) return true;
       if (s_abort) return false;
       __nanosleep(32);
     }
@@ -427,23 +446,20 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
     bool dep_waited = false;
     int it = 0, batch_no = 0;
     int arrived = 0;   // grid barriers this CTA has arrived at (thread 0 only)
-    // Arrive at the barriers that end phases [arrived, upto): thread 0, after every thread's stores of the phase.
+    // Arrive at the barriers that end phases [arrived, upto): thread 0, after every thread's stores of the phase (a CTA
+    // barrier orders those before this thread's fence).  Each barrier has a counter of its own, so a CTA with nothing
+    // to do in a phase need not wait for the barrier before it.
     auto arrive_upto = [&](int upto) {
       upto = min(upto, cp.nphases - 1);   // nothing follows the last phase
-      for (; arrived < upto; ++arrived) {
-        if (!grid_wait(arrived)) {   // the base is recorded and the previous generation is over before this arrival counts
-          if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
-          s_abort = 1;
-        }
-        asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
-        __threadfence();
-        const unsigned int old = atom_add_acq_rel(cp.bar_count, 1u);
-        if (old == (unsigned int)G - 1u) {
-          *reinterpret_cast<volatile unsigned int*>(cp.bar_count) = 0u;
-          __threadfence();
-          atom_add_acq_rel(cp.bar_gen, 1u);
-        }
+      if (arrived >= upto) return;
+      for (uint32_t spin = 0; !s_dep_ok && spin < kGridSpinLimit; ++spin) __nanosleep(100);   // the bases are recorded first
+      if (!s_dep_ok && !s_abort) {
+        s_abort = 1;
+        if (cp.err_flag) atomicExch(cp.err_flag, 6);
       }
+      asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
+      __threadfence();
+      for (; arrived < upto; ++arrived) red_add_release(cp.bar_count + (size_t)arrived * 32, 1u);
     };
     if (tid == 0) arrive_upto(cu.ph);   // phases in which this CTA has nothing to do
 
@@ -466,7 +482,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
 #pragma unroll
       for (int d = 0; d < kGroup; ++d) {
         if (cu.ph >= cp.nphases) break;
-        const int s = it % STAGES;
+        const int s = it % SA;
         if (cu.ph != share_ph) {   // first unit of this CTA's share of a phase
           share_ph = cu.ph;
           share_t0 = cu.tile;
@@ -487,7 +503,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
           iter_next(pf, cp, cta);
         }
         int ok = 1;
-        if (lane == 0) ok = (!s_abort && mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) ? 1 : 0;
+        if (lane == 0) ok = (!s_abort && mbar_wait_dep(a_empty0 + 8 * s, ((it / SA) & 1) ^ 1, &s_dep_ok)) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");   // the MMAs that read this stage are done
@@ -495,7 +511,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
-          if (lane == 0) mbar_arrive(full0 + 8 * s);
+          if (lane == 0) mbar_arrive(a_full0 + 8 * s);
           if (tid == 0) PI_TRACE_FIRST(cp, cta, 8 + cu.ph * 12 + 4);
         } else if (lane == 0 && !s_abort) {
           s_abort = 1;
@@ -519,7 +535,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
             batch.nseg = 0;
             if (share_end) {
               const int nkb = cu.nkb;
-              const int tile_a = share_kb0 != 0 ? share_t0 : ((cu.tile == share_t0 && cu.kb != nkb - 1) ? share_t0 : -1);
+              const int tile_a = (share_kb0 != 0 || (cu.tile == share_t0 && cu.kb != nkb - 1)) ? share_t0 : -1;
               const int tile_b = (cu.kb != nkb - 1 && cu.tile != share_t0) ? cu.tile : -1;
               if (tile_a >= 0 || tile_b >= 0) share_finish<BN>(cp, ec, cu.ph, tile_a, tile_b);
               asm volatile("fence.proxy.async.global;" ::: "memory");   // the next phase reads these stores through TMA
@@ -537,7 +553,7 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
         iter_next(cu, cp, cta);
       }
     }
-    if (tid == 0) arrive_upto(cp.nphases);   // after an abort: keep the barrier consistent for the other CTAs
+    if (tid == 0) arrive_upto(cp.nphases);   // after an abort: keep the barriers consistent for the other CTAs
   } else if (warp == kProducerWarps) {
     // ================= activation loader: one 3-D TMA box {64 K, BN rows, 3 planes} per K atom =====================
     if (lane == 0) {
@@ -547,31 +563,29 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
       int it = 0, ready_ph = -1;
       bool issued = false;
       asm volatile("griddepcontrol.wait;" ::: "memory");   // the first phase's planes come from the preceding kernel
-      s_base_gen = ld_acquire_u32(cp.bar_gen);
+      for (int k = 0; k < kMaxPhases; ++k) s_base[k] = ld_acquire_u32(cp.bar_count + (size_t)k * 32);
       __threadfence_block();
       s_dep_ok = 1;
       PI_TRACE(cp, cta, 1);
       while (cu.ph < cp.nphases) {
         if (cu.ph != ready_ph) {
-          if (cu.ph > 0) {
-            if (!grid_wait(cu.ph)) {   // every CTA has finished the phases before this one
-              if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
-              s_abort = 1;
-              break;
-            }
-            asm volatile("fence.proxy.async.global;" ::: "memory");
+          if (!grid_wait(cu.ph)) {   // every CTA is through with the phases before this one
+            if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 6);
+            s_abort = 1;
+            break;
           }
+          if (cu.ph > 0) asm volatile("fence.proxy.async.global;" ::: "memory");
           ready_ph = cu.ph;
           PI_TRACE(cp, cta, 8 + cu.ph * 12 + 0);
         }
-        const int s = it % STAGES;
+        const int s = it % SB;
         if (s_abort) break;
-        if (!mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) {
+        if (!mbar_wait_dep(b_empty0 + 8 * s, ((it / SB) & 1) ^ 1, &s_dep_ok)) {
           s_abort = 1;
           if (cp.err_flag) atomicExch(cp.err_flag, 3);
           break;
         }
-        const uint32_t bar = full0 + 8 * s;
+        const uint32_t bar = b_full0 + 8 * s;
         const uint32_t b_stage = smem_base + s * kBStageBytes;
 #ifdef PI_CHAIN_DBG_NO_B
         mbar_arrive(bar);
@@ -598,15 +612,15 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
   } else {
     // ================= MMA issuer ==================================================================================
     if (lane == 0) {
-      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = bf16, M = 128, N = BN: the three planes of a K step are
-      // three MMAs into the same accumulator columns
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      // kind::f16, D = f32, A (TMEM) and B (shared, K-major) = bf16, M = 128, N = 3*BN: one MMA per K step leaves
+      // W*p0, W*p1, W*p2 in the three column groups of the segment's accumulator
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kSegCols >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       UnitIter cu;
       cu.ph = 0;
       iter_enter(cu, cp, cta);
       int it = 0, nseg = 0, batch_no = 0;
       while (cu.ph < cp.nphases) {
-        const int s = it % STAGES;
+        const int sa = it % SA, sb = it % SB;
         if (cu.first && nseg == 0 && batch_no > 0) {   // the accumulators of the previous batch have been taken out
           if (s_abort || !mbar_wait_dep(accum_empty, (uint32_t)((batch_no - 1) & 1), &s_dep_ok)) {
             if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 7);
@@ -614,28 +628,27 @@ gemm_chain_kernel(const __grid_constant__ ChainParams cp, const __grid_constant_
             break;
           }
         }
-        if (s_abort || !mbar_wait_dep(full0 + 8 * s, (it / STAGES) & 1, &s_dep_ok)) {
+        if (s_abort || !mbar_wait_dep(b_full0 + 8 * sb, (it / SB) & 1, &s_dep_ok) ||
+            !mbar_wait_dep(a_full0 + 8 * sa, (it / SA) & 1, &s_dep_ok)) {
           if (!s_abort && cp.err_flag) atomicExch(cp.err_flag, 4);
           s_abort = 1;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         PI_TRACE_FIRST(cp, cta, 8 + cu.ph * 12 + 2);
-        const uint32_t stage_addr = smem_base + s * kBStageBytes;
-        const uint32_t a_s = tmem_a0 + (uint32_t)(s * kACols);
-        const uint32_t d_seg = tmem + (uint32_t)(nseg * BN);
+        const uint64_t db0 = smem_desc(smem_base + sb * kBStageBytes);
+        const uint32_t a_s = tmem_a0 + (uint32_t)(sa * kACols);
+        const uint32_t d_seg = tmem + (uint32_t)(nseg * kSegCols);
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {  // 16 K elements: 8 TMEM columns of A, 32 bytes of every B row
-#pragma unroll
-            for (int pl = 0; pl < kPlanes; ++pl) {
-              const uint64_t db = smem_desc(stage_addr + atom * kBAtomBytes + pl * kPlaneBytes) + (uint64_t)((ks * 32) >> 4);
-              umma_f16_ts(d_seg, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (!cu.first || atom + ks + pl > 0) ? 1u : 0u);
-            }
+            const uint64_t db = db0 + (uint64_t)((atom * kBAtomBytes + ks * 32) >> 4);
+            umma_f16_ts(d_seg, a_s + (uint32_t)((atom * 4 + ks) * 8), db, idesc, (!cu.first || atom + ks > 0) ? 1u : 0u);
           }
         }
-        umma_commit(empty0 + 8 * s);  // the stage (TMEM columns and shared tile) is free once these MMAs are done
+        umma_commit(a_empty0 + 8 * sa);  // the weight stage (TMEM columns) and the activation stage (shared memory)
+        umma_commit(b_empty0 + 8 * sb);  // are free once these MMAs are done
         if (iter_seg_last(cu)) {
           ++nseg;
           if (cu.left == 1 || nseg == kMaxSegs) {
@@ -676,10 +689,10 @@ ChainQueue* queue_of(pi_ctx* ctx) {
   return static_cast<ChainQueue*>(ctx->gemm_chain);
 }
 
-template <int BN, int STAGES>
+template <int BN, int SA, int SB>
 cudaError_t launch_chain(pi_ctx* ctx, const ChainQueue& q, int grid) {
-  constexpr size_t smem = (size_t)STAGES * (2 * kPlanes * BN * 128) + (size_t)BN * kBM * sizeof(float) + 1024;
-  auto k = gemm_chain_kernel<BN, STAGES>;
+  constexpr size_t smem = (size_t)SB * (2 * kPlanes * BN * 128) + (size_t)BN * kBM * sizeof(float) + 1024;
+  auto k = gemm_chain_kernel<BN, SA, SB>;
   static pi_smem_grant granted;  // per instantiation
   if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -740,16 +753,16 @@ pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
     q->ws_slots = std::max(slots, q->ws_slots);
     q->ws_tiles = std::max(tiles, q->ws_tiles);
     q->ws_bn = std::max(BN, q->ws_bn);
-    const size_t bytes = q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float) + (2 * q->ws_tiles + 64) * sizeof(unsigned int);
+    const size_t bytes = q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float) + (4 * q->ws_tiles + 32 * kMaxPhases) * sizeof(unsigned int);
     PI_CUDA(ctx, cudaMalloc(&q->ws, bytes));
     PI_CUDA(ctx, cudaMemsetAsync(q->ws, 0, bytes, ctx->stream));
   }
   q->cp.partials = static_cast<float*>(q->ws);
   unsigned int* words = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(q->ws) + q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float));
-  q->cp.bar_count = words;          // a 128-byte line of its own
-  q->cp.bar_gen = words + 32;
-  q->cp.tickets = words + 64;
-  q->cp.done = words + 64 + q->ws_tiles;
+  q->cp.bar_count = words;          // one 128-byte line per barrier
+  q->cp.tickets = words + 32 * kMaxPhases;
+  q->cp.done = q->cp.tickets + 2 * q->ws_tiles;
+  q->cp.max_tiles = (int)q->ws_tiles;
 #ifdef PI_CHAIN_TRACE
   static unsigned long long* trace_dev = nullptr;
   const size_t trace_bytes = (size_t)256 * 64 * sizeof(unsigned long long);
@@ -759,9 +772,9 @@ pi_status pi_gemm_chain_flush(pi_ctx* ctx) {
 #endif
   cudaError_t err;
   switch (BN) {
-    case 16: err = launch_chain<16, 6>(ctx, *q, grid); break;
-    case 32: err = launch_chain<32, 6>(ctx, *q, grid); break;
-    default: err = launch_chain<64, 4>(ctx, *q, grid); break;
+    case 16: err = launch_chain<16, 6, 4>(ctx, *q, grid); break;    // TMEM: 2 x 48 accumulator columns, weights from 128
+    case 32: err = launch_chain<32, 5, 4>(ctx, *q, grid); break;    //       2 x 96, weights from 192
+    default: err = launch_chain<64, 2, 3>(ctx, *q, grid); break;    //       2 x 192, weights from 384
   }
   if (err != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "projection chain launch (%d phases) failed: %s", n, cudaGetErrorString(err));
   ctx->launches++;
@@ -796,7 +809,7 @@ void pi_gemm_chain_reset_sync(pi_ctx* ctx) {
   ChainQueue* q = static_cast<ChainQueue*>(ctx->gemm_chain);
   if (!q || !q->ws) return;
   unsigned char* words = static_cast<unsigned char*>(q->ws) + q->ws_slots * (size_t)q->ws_bn * kBM * sizeof(float);
-  cudaMemsetAsync(words, 0, (2 * q->ws_tiles + 64) * sizeof(unsigned int), ctx->stream);
+  cudaMemsetAsync(words, 0, (4 * q->ws_tiles + 32 * kMaxPhases) * sizeof(unsigned int), ctx->stream);
 }
 
 void pi_gemm_chain_destroy(pi_ctx* ctx) {
