@@ -502,8 +502,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
                 "gemv": weight_bytes / max(prof["gemv"][1] / P, 1), "gemm_tc": weight_bytes / max(prof["gemm_tc"][1] / P, 1)}
         names = {"attention": "attn_decode_v3_kernel<64,8,3> (+ split merge): one layer, 64 sequences",
                  "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step",
-                 "gemm_tc": "gemm_chain_kernel<64,4>: the step's tcgen05 dequant projections, up to four consecutive ones "
-                            "(o, gate/up, down, next q/k/v or the LM head) as phases of one persistent launch"}
+                 "gemm_tc": "gemm_ta_kernel<64,4>: tcgen05 dequant projections of the step (average over its launches)"}
         rl = {}
         for cls in ("attention", "gemv", "gemm_tc"):
             ms, n = prof[cls]
@@ -829,27 +828,6 @@ def run_kernel_case(args):
         e1.record()
         torch.cuda.synchronize()
         algo = B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 + 2 * qv.numel() * 4
-    elif case == "decode_chain":
-        # a two-layer cut of the default model, 64 sequences at 512 tokens: a few whole decode steps, whose projections
-        # leave as persistent chain launches (q/k/v | o, gate/up, down, q/k/v | o, gate/up, down, LM head)
-        cfgd = dict(TINYLLAMA)
-        cfgd["num_hidden_layers"] = 2
-        cfg = LlamaConfig(**cfgd, quantization="int8")
-        model = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=64, max_positions=1024)
-        B, ctx_len = 64, 512
-        nblk = ctx_len // BLOCK + 2
-        kv = api.KvCache(ctx, model.kv_layout(B * nblk, BLOCK))
-        kv.fill_normal(9, 1.0)
-        tables = [list(range(b * nblk, (b + 1) * nblk)) for b in range(B)]
-        tok = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
-        model.decode_multi(tok, [ctx_len] * B, tables, kv, 2)
-        torch.cuda.synchronize()
-        e0.record()
-        for r in range(reps):
-            model.decode_multi(tok, [ctx_len] * B, tables, kv, 1)
-        e1.record()
-        torch.cuda.synchronize()
-        algo = model.weight_bytes() + B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 * cfg.num_hidden_layers
     elif case == "attention_prefill":
         # the last 512-position chunk of a 2048-token prompt: every entry maps the same table
         cfg = LlamaConfig(**TINYLLAMA, quantization="int8")
@@ -889,7 +867,7 @@ def run_kernel_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel-case", default=None,
-                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention", "attention_prefill", "decode_chain"],
+                    choices=["gemv_lm_head", "gemm_lm_head", "gemm_gate_up", "gemm_down", "attention", "attention_prefill"],
                     help="run a few launches of one kernel on a small case (for a profiler) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -28,7 +28,7 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
     # no --use_fast_math: the quantiser needs IEEE division and rounding
-] + os.environ.get("PI_NVCC_EXTRA", "").split()   # e.g. -DPI_CHAIN_TRACE for the per-CTA timeline of pi_gemm_chain.cu
+]
 
 
 def nvcc() -> str:

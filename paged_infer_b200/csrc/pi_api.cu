@@ -75,7 +75,6 @@ static pi_status check_device_flag(pi_ctx* ctx) {
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (flag != 0) {
     PI_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
-    pi_gemm_chain_reset_sync(ctx);   // a persistent kernel that wound down early may have left its barrier mid-count
     if (flag == 9) {
       // a peer never delivered its partial sums: the slots of the ranks are out of step from here on, so the
       // peer-memory exchange is retired and later steps go through NCCL (or fail loudly without a communicator)
@@ -161,7 +160,6 @@ void pi_ctx_destroy(pi_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   pi_tp_destroy(ctx);
-  pi_gemm_chain_destroy(ctx);
   for (pi_buffer* b : {&ctx->staging_in, &ctx->staging_out, &ctx->attn_tables, &ctx->attn_partial, &ctx->gemm_act})
     if (b->ptr) cudaFree(b->ptr);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
@@ -173,7 +171,6 @@ void pi_ctx_destroy(pi_ctx* ctx) {
 
 pi_status pi_ctx_synchronize(pi_ctx* ctx) {
   if (!ctx) return PI_ERR_INVALID_ARG;
-  PI_TRY(pi_gemm_chain_flush(ctx));
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return check_device_flag(ctx);
 }
@@ -220,10 +217,6 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_ATTN_TMA: ctx->opt_attn_tma = value; return PI_OK;
     case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
-    case PI_OPT_GEMM_CHAIN:
-      PI_TRY(pi_gemm_chain_flush(ctx));
-      ctx->opt_gemm_chain = value != 0;
-      return PI_OK;
     case PI_OPT_PEER_SPIN_LIMIT:
       PI_REQUIRE(ctx, value >= 0, "the spin limit cannot be negative");
       ctx->peer_spin_limit = (uint32_t)value;

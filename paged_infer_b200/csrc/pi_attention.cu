@@ -897,7 +897,6 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
 pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
                               size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch,
                               pi_act_planes* emit, bool* emitted) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   if (emitted) *emitted = false;
   const pi_kv_layout& L = pool->L;
   PI_REQUIRE(ctx, layer >= 0 && layer < L.num_layers, "layer %d outside the pool's %d layers", layer, L.num_layers);

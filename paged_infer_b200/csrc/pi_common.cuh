@@ -86,7 +86,6 @@ struct pi_ctx {
   int opt_gemv_max_m = 4;
   int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always, 3 always and on the mma.sync kernel
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
-  bool opt_gemm_chain = true;   // batches of up to 64 rows: consecutive projections run as phases of one persistent launch
   int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
@@ -100,7 +99,6 @@ struct pi_ctx {
   pi_buffer attn_tables;               // block tables + per-entry (len, pos, start)
   pi_buffer attn_partial;              // split-KV partial (m, l, acc)
   pi_buffer gemm_act;                  // bf16 activation planes (+ row factors) for the tensor GEMM
-  void* gemm_chain = nullptr;          // queue + scratch of the persistent projection-chain kernel (pi_gemm_chain.cu)
   void* pinned = nullptr;              // pinned host staging
   size_t pinned_bytes = 0;
 };
@@ -198,17 +196,6 @@ bool pi_gemm_tc_can_emit(const pi_ctx* ctx, const pi_linear* lin, const pi_linea
 bool pi_gemm_tc_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r);
 // The same for the CUDA-core path (any head_dim that is even).
 bool pi_gemv_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_rope_kv& r);
-// The persistent kernel for batches of up to 64 activation rows (pi_gemm_chain.cu).  Between open and close,
-// projections that qualify are queued instead of launched and go out together - up to four as consecutive phases of
-// ONE launch - at the next flush.  Every launcher of another kernel on the context's stream flushes first, so stream
-// order is what the call order says.  Outside open/close a queued projection is launched at once.
-bool pi_gemm_chain_usable(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a);
-pi_status pi_gemm_chain_enqueue(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, const pi_act_planes& in);
-void pi_gemm_chain_open(pi_ctx* ctx);
-pi_status pi_gemm_chain_flush(pi_ctx* ctx);
-pi_status pi_gemm_chain_close(pi_ctx* ctx);
-void pi_gemm_chain_reset_sync(pi_ctx* ctx);
-void pi_gemm_chain_destroy(pi_ctx* ctx);
 // The activation split on its own (what the GEMM runs first when it is not given planes): x -> planes in `dst`.
 pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, const float* norm_weight, float eps, int M, int K,
                               pi_act_planes* dst);

@@ -676,16 +676,10 @@ pi_status pi_launch_act_split(pi_ctx* ctx, const float* x, size_t x_stride, cons
 
 pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
   PI_REQUIRE(ctx, pi_gemm_tc_supported(ctx, lin, a), "tensor-core GEMM does not support this projection");
-  const bool chain = pi_gemm_chain_usable(ctx, lin, a);   // up to 64 activation rows: the persistent kernel
   if (a.in_planes) {
-    if (chain) return pi_gemm_chain_enqueue(ctx, lin, a, *a.in_planes);
-    PI_TRY(pi_gemm_chain_flush(ctx));
     pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
     return run_gemm(ctx, lin, a, *a.in_planes);
   }
-  // The activations must be split first: a kernel of its own, so whatever is queued goes out before it (a queued
-  // projection may also still read the scratch that the split is about to overwrite).
-  PI_TRY(pi_gemm_chain_flush(ctx));
   const int M = a.M, K = (int)lin->cols;
   // scratch (global memory beyond the inputs and outputs): the planes and the row factors
   PI_TRY(pi_reserve(ctx, &ctx->gemm_act, (size_t)kPlanes * M * K * sizeof(__nv_bfloat16) + (size_t)M * sizeof(float) + 256));
@@ -694,7 +688,6 @@ pi_status pi_launch_gemm_tc(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
     pi_prof_scope prof(ctx, PI_PROF_OTHER);
     PI_TRY(pi_launch_act_split(ctx, a.x, a.x_stride, a.norm_weight, a.norm_eps, M, K, &pl));
   }
-  if (chain) return pi_gemm_chain_enqueue(ctx, lin, a, pl);
   pi_prof_scope prof(ctx, PI_PROF_GEMM_TC);
   return run_gemm(ctx, lin, a, pl);
 }

@@ -1,7 +1,6 @@
-// Device helpers shared by the tcgen05 dequant GEMM kernels (pi_gemm_tc.cu: one launch per projection, clusters for
-// split K; pi_gemm_chain.cu: one persistent launch for a chain of projections): mbarrier / TMEM / MMA wrappers in
-// inline PTX, the exact int8 -> bf16 widening, the launch parameters of one projection and its epilogues (store /
-// residual add / SwiGLU, planes for the next projection, rotary embedding + KV write).
+// Device side of the tcgen05 dequant GEMM (pi_gemm_tc.cu): mbarrier / TMEM / MMA wrappers in inline PTX, the exact
+// int8 -> bf16 widening, the launch parameters of one projection and its epilogues (store / residual add / SwiGLU,
+// planes for the next projection, rotary embedding + KV write).
 #pragma once
 
 #include <cuda.h>

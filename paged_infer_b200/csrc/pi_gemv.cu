@@ -571,7 +571,6 @@ bool pi_gemv_can_rope(const pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
 }
 
 pi_status pi_launch_gemv(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   PI_REQUIRE(ctx, a.M >= 1, "projection batch must be at least 1");
   PI_REQUIRE(ctx, a.epi != PI_EPI_SWIGLU || lin->rows % 2 == 0, "SwiGLU epilogue needs interleaved gate/up rows");
   if (lin->rows == 0) return PI_OK;

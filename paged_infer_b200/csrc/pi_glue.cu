@@ -282,14 +282,12 @@ void pi_host_rope_table(int pos, int head_dim, float theta, float* cos_out, floa
 
 pi_status pi_launch_embed(pi_ctx* ctx, const uint16_t* table_bf16, int vocab, int hidden, const uint32_t* tokens_dev,
                           int B, float* x) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
   PI_LAUNCHED(ctx, launch_pdl(ctx, embed_kernel, dim3(B), dim3(256), table_bf16, vocab, hidden, tokens_dev, x));
   return PI_OK;
 }
 
 pi_status pi_launch_rms_norm(pi_ctx* ctx, float* x, size_t stride, const float* weight, int rows, int n, float eps) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   rms_norm_kernel<<<rows, 256, 0, ctx->stream>>>(x, stride, weight, n, eps);
   PI_CHECK_LAUNCH(ctx);
   return PI_OK;
@@ -298,7 +296,6 @@ pi_status pi_launch_rms_norm(pi_ctx* ctx, float* x, size_t stride, const float* 
 pi_status pi_launch_rope_kv_write(pi_ctx* ctx, float* qkv, size_t qkv_stride, int num_heads, int num_kv_heads,
                                   int head_dim, const float* rope_cos, const float* rope_sin, int style,
                                   pi_kv_pool* pool, int layer, const pi_attn_batch& batch) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
   pi_prof_scope prof(ctx, PI_PROF_ROPE_KV);
   PI_LAUNCHED(ctx, launch_pdl(ctx, rope_kv_write_kernel, dim3(num_heads + num_kv_heads, batch.B), dim3(threads), qkv,
@@ -322,7 +319,6 @@ pi_status pi_launch_swiglu(pi_ctx* ctx, float* gate, const float* up, size_t n) 
 }
 
 pi_status pi_launch_add(pi_ctx* ctx, float* x, const float* y, size_t n) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
   if (n == 0) return PI_OK;
   PI_LAUNCHED(ctx, launch_pdl(ctx, add_kernel, dim3(grid_for(n, 256, ctx->sm_count)), dim3(256), x, y, n));
@@ -330,14 +326,12 @@ pi_status pi_launch_add(pi_ctx* ctx, float* x, const float* y, size_t n) {
 }
 
 pi_status pi_launch_argmax(pi_ctx* ctx, const float* logits, size_t stride, int rows, int n, uint32_t* out) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
   PI_LAUNCHED(ctx, launch_pdl(ctx, argmax_kernel, dim3(rows), dim3(1024), logits, stride, n, out));
   return PI_OK;
 }
 
 pi_status pi_launch_copy_block(pi_ctx* ctx, pi_kv_pool* pool, int src, int dst) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   const size_t bs = pool->block_stride();
   const size_t layer_stride = bs * pool->L.num_blocks;
   unsigned chunks = (unsigned)((bs / 4 + 255) / 256);

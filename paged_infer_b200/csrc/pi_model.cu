@@ -314,21 +314,6 @@ __global__ void gather_logits_kernel(const float* __restrict__ in, float* __rest
   }
 }
 
-// Between construction and close() (or destruction, on an error path) the projections of the forward pass are queued
-// and leave as phases of one persistent launch each time another kernel has to come between them.
-struct chain_scope {
-  pi_ctx* ctx;
-  bool closed = false;
-  explicit chain_scope(pi_ctx* c) : ctx(c) { pi_gemm_chain_open(c); }
-  pi_status close() {
-    closed = true;
-    return pi_gemm_chain_close(ctx);
-  }
-  ~chain_scope() {
-    if (!closed) pi_gemm_chain_close(ctx);
-  }
-};
-
 // What the last projection of run_layers left for the LM head when it could emit planes (tp == 1, tensor path).
 struct x_planes_state {
   pi_act_planes planes;
@@ -685,12 +670,8 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
   pi_attn_batch batch;
   PI_TRY(stage_batch(ctx, m, pool, tokens_host, positions_host, block_tables_host, max_blocks, table_lens_host, B, &batch));
   x_planes_state xs;
-  {
-    chain_scope chain(ctx);
-    PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
-    PI_TRY(project_logits(ctx, m, 0, B, &xs));
-    PI_TRY(chain.close());
-  }
+  PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
+  PI_TRY(project_logits(ctx, m, 0, B, &xs));
   PI_TRY(fetch_results(ctx, m, B, logits_host_or_null, argmax_host_or_null));
   if (logits_host_or_null || argmax_host_or_null) return pi_ctx_synchronize(ctx);
   return PI_OK;
@@ -726,12 +707,8 @@ static __global__ void next_step_kernel(int* step_counter) {
 static pi_status decode_one_step(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_batch& batch, int B,
                                  uint32_t* history, int* step_counter) {
   x_planes_state xs;
-  {
-    chain_scope chain(ctx);
-    PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
-    PI_TRY(project_logits(ctx, m, 0, B, &xs));
-    PI_TRY(chain.close());
-  }
+  PI_TRY(run_layers(ctx, m, pool, batch, B, &xs));
+  PI_TRY(project_logits(ctx, m, 0, B, &xs));
   PI_TRY(pi_launch_argmax(ctx, m->logits, m->cfg.vocab_size, B, m->cfg.vocab_size, m->argmax_dev));
   pi_prof_scope prof(ctx, PI_PROF_OTHER);
   const int blocks = (B + 127) / 128;
@@ -839,9 +816,7 @@ pi_status pi_model_prefill(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uin
     }
     pi_attn_batch batch;
     PI_TRY(stage_batch(ctx, m, pool, tokens_host + c0, pos.data(), tables.data(), table_len, lens.data(), len, &batch));
-    chain_scope chain(ctx);
     PI_TRY(run_layers(ctx, m, pool, batch, len, nullptr));
-    PI_TRY(chain.close());
     last_rows = len;
   }
   PI_TRY(project_logits(ctx, m, last_rows - 1, 1));

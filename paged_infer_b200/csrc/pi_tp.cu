@@ -95,7 +95,6 @@ void pi_tp_destroy(pi_ctx* ctx) {
 }
 
 pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   if (ctx->tp == 1 || n == 0) return PI_OK;
   if (!ctx->nccl_comm) return pi_fail(ctx, PI_ERR_NCCL, "this tensor-parallel context has no NCCL communicator (created without a unique id) and its peer-memory exchange is not usable");
   pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
@@ -104,7 +103,6 @@ pi_status pi_tp_all_reduce_sum(pi_ctx* ctx, float* buf, size_t n) {
 }
 
 pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t bytes_per_rank) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   if (ctx->tp == 1) {
     PI_CUDA(ctx, cudaMemcpyAsync(recv, send, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
     return PI_OK;
@@ -331,7 +329,6 @@ float* pi_tp_peer_slot(pi_ctx* ctx) { return ctx->peer.data[ctx->rank] + (size_t
 
 pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_act_planes* emit, const float* emit_norm_weight,
                                 float emit_norm_eps) {
-  PI_TRY(pi_gemm_chain_flush(ctx));
   const size_t n = (size_t)rows * cols;
   PI_REQUIRE(ctx, pi_tp_peer_usable(ctx, n) && cols % 4 == 0 && (uintptr_t)x % 16 == 0, "the peer exchange is not set up for %zu values", n);
   pi_prof_scope prof(ctx, PI_PROF_COLLECTIVE);
