@@ -170,7 +170,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_shared_tc_kernel(const TcA
   const uint32_t kv_full0 = s_u32(&bars[0]), kv_free0 = s_u32(&bars[kStagesTc]), s_full0 = s_u32(&bars[2 * kStagesTc]),
                  p_full0 = s_u32(&bars[2 * kStagesTc + 2]), o_full = s_u32(&bars[2 * kStagesTc + 4]),
                  o_free = s_u32(&bars[2 * kStagesTc + 5]);
-  pi_grid_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < kStagesTc; ++i) {
       bar_init(kv_full0 + 8 * i, 4);   // one arrival per converter warp
@@ -194,6 +193,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_shared_tc_kernel(const TcA
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // the dependent grid is released only now that this CTA holds its tensor memory (a dependent CTA that took the
+  // SM's columns first would keep them until this grid completes)
+  pi_grid_launch_dependents();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem;
   const uint32_t smem_base = s_u32(smem);

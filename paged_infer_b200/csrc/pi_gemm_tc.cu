@@ -67,6 +67,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
   __shared__ uint32_t s_tmem;
   __shared__ volatile int s_abort;
+  __shared__ volatile int s_dep_ok;   // the preceding kernel has completed: from here on waits are this kernel's own
   __shared__ float s_rowf[BN];     // row factor of the activation rows of this CTA
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -74,9 +75,6 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   const int row0 = blockIdx.x * kBM, m0 = blockIdx.z * BN;
   const int kb_begin = (int)((long)blockIdx.y * p.nkb / p.ksplit), kb_end = (int)((long)(blockIdx.y + 1) * p.nkb / p.ksplit);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
-  // Every thread releases the dependent grid right away (the release only happens once all threads of all CTAs
-  // have done so): the next kernels then sit resident, with their own prologue done, by the time this one ends.
-  pi_grid_launch_dependents();
 
   // ---- weight producers (warps 0-15): thread = weight row quad*32+lane, K quarter `kq` of every K block --------
   // A GROUP of kGroup K blocks (32 bytes each) is requested one group ahead of the one being widened; the first
@@ -102,6 +100,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
     }
     mbar_init(accum_bar, 1);
     s_abort = 0;
+    s_dep_ok = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -112,6 +111,11 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // Every thread releases the dependent grid (the release only happens once all threads of all CTAs have done so):
+  // the next kernels then sit resident, with their own prologue done, by the time this one ends.  Only now that this
+  // CTA holds its tensor memory: a dependent CTA that took the SM's columns first would keep them until this grid
+  // completes, and this CTA would wait for them for ever.
+  pi_grid_launch_dependents();
   const uint32_t tmem = s_tmem;
   const uint32_t tmem_a0 = tmem + (uint32_t)kAStart;
   const uint32_t smem_base = smem_u32(smem);
@@ -131,7 +135,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
         for (int i = 0; i < 8; ++i) widen4(cur[d][i], h[2 * i], h[2 * i + 1]);
         // lane 0 polls for the whole warp
         int ok = 1;
-        if (lane == 0) ok = (!s_abort && mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) ? 1 : 0;
+        if (lane == 0) ok = (!s_abort && mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) {
           if (lane == 0 && !s_abort) {
@@ -161,10 +165,11 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
     // ---- activation loader: one 3-D TMA box {64 K, BN rows, 3 planes} per K atom -------------------------------
     if (lane == 0) {
       pi_grid_dependency_wait();  // the activation planes come from the preceding kernel
+      s_dep_ok = 1;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int it = kb - kb_begin, s = it % STAGES;
         if (s_abort) break;
-        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) {
+        if (!mbar_wait_dep(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &s_dep_ok)) {
           s_abort = 1;
           if (p.err_flag) atomicExch(p.err_flag, 3);
           break;
@@ -190,7 +195,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
       bool ok = true;
       for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int it = kb - kb_begin, s = it % STAGES;
-        if (s_abort || !mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) {
+        if (s_abort || !mbar_wait_dep(full0 + 8 * s, (it / STAGES) & 1, &s_dep_ok)) {
           if (!s_abort && p.err_flag) atomicExch(p.err_flag, 4);
           s_abort = 1;
           ok = false;
@@ -218,7 +223,7 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   if (warp < kParkWarps) {
     int got = 0;
     if (lane == 0) {
-      got = ((kb_begin < kb_end) && !s_abort && mbar_wait(accum_bar, 0)) ? 1 : 0;
+      got = ((kb_begin < kb_end) && !s_abort && mbar_wait_dep(accum_bar, 0, &s_dep_ok)) ? 1 : 0;
       if (kb_begin < kb_end && !got && !s_abort) {
         s_abort = 1;
         if (p.err_flag) atomicExch(p.err_flag, 5);

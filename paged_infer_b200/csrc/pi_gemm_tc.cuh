@@ -81,6 +81,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// The same, for kernels that start before the kernel ahead of them in the stream has finished (programmatic dependent
+// launch): polls are only counted once `*dep_ok` says that this launch's dependency is resolved.  Until then nothing
+// here can make progress and the wait is the preceding kernel's, however long that runs - it must not be mistaken for
+// a wait of this kernel that ran out.
+__device__ __forceinline__ bool mbar_wait_dep(uint32_t bar, uint32_t parity, const volatile int* dep_ok) {
+  for (uint32_t spin = 0; spin < kSpinLimit;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*dep_ok) ++spin;
+  }
+  return false;
+}
+
 __device__ __forceinline__ void ld_stream_32(const void* p, uint32_t* v) {
   asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])

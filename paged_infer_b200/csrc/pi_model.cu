@@ -44,6 +44,10 @@ struct pi_model {
   float* sumsq = nullptr;
   int sumsq_tiles_cap = 0;
   size_t weight_bytes = 0;
+  // pi_model_decode_multi: the executable graph of one decode step, kept between calls.  Every call captures its step
+  // anew (the launch parameters depend on the batch) and updates this executable in place, which is much cheaper than
+  // instantiating one; only a change of topology (another batch shape, another kernel choice) rebuilds it.
+  cudaGraphExec_t step_exec = nullptr;
 };
 
 namespace {
@@ -619,6 +623,7 @@ pi_status pi_model_create_synthetic(pi_ctx* ctx, const pi_model_config* cfg, uin
 
 void pi_model_destroy(pi_model* m) {
   if (!m) return;
+  if (m->step_exec) cudaGraphExecDestroy(m->step_exec);
   for (auto* v : {&m->qkv, &m->wo, &m->gate_up, &m->down})
     for (pi_linear* l : *v) pi_linear_destroy(l);
   pi_linear_destroy(m->lm_head);
@@ -763,7 +768,6 @@ pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
   int done = 1;
   if (ctx->opt_graph && !ctx->prof_on && n_steps >= 4) {
     cudaGraph_t graph = nullptr;
-    cudaGraphExec_t exec = nullptr;
     const uint64_t before = ctx->launches;
     cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
     if (e == cudaSuccess) {
@@ -771,15 +775,24 @@ pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
       e = cudaStreamEndCapture(ctx->stream, &graph);
       const uint64_t per_step = ctx->launches - before;
       ctx->launches = before;
-      if (st == PI_OK && e == cudaSuccess && graph) e = cudaGraphInstantiate(&exec, graph, 0);
-      if (st == PI_OK && e == cudaSuccess && exec) {
+      if (st == PI_OK && e == cudaSuccess && graph) {
+        if (m->step_exec) {   // same topology as last time: new parameters into the old executable
+          cudaGraphExecUpdateResultInfo info;
+          if (cudaGraphExecUpdate(m->step_exec, graph, &info) != cudaSuccess) {
+            cudaGetLastError();
+            cudaGraphExecDestroy(m->step_exec);
+            m->step_exec = nullptr;
+          }
+        }
+        if (!m->step_exec) e = cudaGraphInstantiate(&m->step_exec, graph, 0);
+      }
+      if (st == PI_OK && e == cudaSuccess && m->step_exec) {
         for (; done < n_steps; ++done) {
-          e = cudaGraphLaunch(exec, ctx->stream);
+          e = cudaGraphLaunch(m->step_exec, ctx->stream);
           if (e != cudaSuccess) break;
           ctx->launches += per_step;
         }
       }
-      if (exec) cudaGraphExecDestroy(exec);
       if (graph) cudaGraphDestroy(graph);
       if (st != PI_OK) return st;
     }
