@@ -683,284 +683,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
   }
 }
 
-// ---- the same, two warps per tile ------------------------------------------------------------------------------
-//
-// attn_decode_v3_kernel keeps the query and the accumulator of all G heads of a KV head in every lane: 128 of its
-// ~190 registers, which leaves room for only two CTAs of four warps on an SM, and two warps per scheduler cannot hide
-// the latency of their own shuffle / shared-load / FMA chains (issue slots 42 % busy, DRAM half used).  Here the two
-// warps of a PAIR work on the same K|V tile, each for half of the query heads: half the registers per thread, so
-// four CTAs (16 warps) fit an SM, with the same bytes in flight per SM (one ring of tiles per pair, filled by bulk
-// copies that the pair's first warp issues and both warps wait for; a slot is refilled once both have left it).
-// Everything else - tile-at-a-time softmax in the log2 domain, reduce-scatter of the head scores over the lanes of a
-// token, rescale only when a maximum moved, log-sum-exp merge of warps and KV splits - is as above.
-constexpr int kPairWarps = 4;   // two pairs per CTA
-
-template <int HD, int G, int STAGES>
-__global__ void __launch_bounds__(kPairWarps * 32, 4) attn_decode_pair_kernel(const AttnParams p) {
-  static_assert(G % 2 == 0, "a pair splits the query heads of a KV head in two");
-  constexpr int GW = G / 2;         // heads per warp
-  constexpr int BS = 16;
-  constexpr int LPT = HD / 8;       // lanes per token
-  constexpr int TPW = 32 / LPT;     // tokens per warp step
-  constexpr int STEPS = BS / TPW;   // steps per tile
-  constexpr int kPairs = kPairWarps / 2;
-  constexpr uint32_t kTileBytes = 2u * BS * HD * sizeof(float);
-  constexpr float kLog2e = 1.4426950408889634f;
-  extern __shared__ __align__(128) unsigned char attn_smem[];
-  __shared__ __align__(8) unsigned long long full[kPairs][STAGES], empty[kPairs][STAGES];
-  __shared__ float s_m[kPairWarps][GW], s_l[kPairWarps][GW];
-
-  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int pair = warp >> 1, hw = warp & 1;     // which tiles, which half of the heads
-  const int tg = lane / LPT, li = lane % LPT;
-  float* ring = reinterpret_cast<float*>(attn_smem) + (size_t)pair * STAGES * (kTileBytes / 4);
-
-  if (hw == 0 && lane == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(attn_smem_u32(&full[pair][s])));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(attn_smem_u32(&empty[pair][s])));
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncthreads();
-  pi_grid_dependency_wait();
-
-  const int pos = p.pos[b], st = p.start[b], len = p.lens[b];
-  const int lb_first = st / BS, lb_last = pos / BS;
-  const int lb_begin = lb_first + split * p.blocks_per_cta;
-  const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);
-  const int nblk = (st <= pos && lb_begin + pair < lb_end) ? (lb_end - lb_begin - pair + kPairs - 1) / kPairs : 0;
-  const bool issuer = hw == 0 && lane == 0;
-
-  auto lookup = [&](int j) { return p.tables[(size_t)b * p.max_blocks + lb_begin + pair + j * kPairs]; };
-  auto issue = [&](int j, int pb) {
-    const float* src = p.kv + pi_kv_tile_offset(p.L, p.layer, pb, kvh, 0);
-    const uint32_t bar = attn_smem_u32(&full[pair][j % STAGES]);
-    const uint32_t dst = attn_smem_u32(ring + (size_t)(j % STAGES) * (kTileBytes / 4));
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kTileBytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(kTileBytes), "r"(bar)
-                 : "memory");
-  };
-  auto wait_bar = [&](uint32_t bar, uint32_t parity) {
-    uint32_t done = 0;
-    for (uint32_t spin = 0; spin < kAttnSpinLimit && !done; ++spin)
-      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                   : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-  };
-  int pb_next = -1;
-  if (issuer) {
-    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j, lookup(j));
-    if (STAGES < nblk) pb_next = lookup(STAGES);
-  }
-
-  // q: 8 dims per lane (16-byte chunks li and li + LPT of the head) for this warp's heads, as float2 pairs
-  float2 qv[GW][4];
-  const float* qb = p.q + (size_t)b * p.q_stride + (size_t)(kvh * G + hw * GW) * HD;
-#pragma unroll
-  for (int g = 0; g < GW; ++g) {
-    const float4 a = ldg_f4(qb + g * HD + li * 4), c = ldg_f4(qb + g * HD + (li + LPT) * 4);
-    qv[g][0] = make_float2(a.x, a.y); qv[g][1] = make_float2(a.z, a.w);
-    qv[g][2] = make_float2(c.x, c.y); qv[g][3] = make_float2(c.z, c.w);
-  }
-  float2 acc[GW][4];
-#pragma unroll
-  for (int g = 0; g < GW; ++g)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[g][i] = make_float2(0.f, 0.f);
-  float m_own = -INFINITY, l_own = 0.f;
-  const float scale2 = p.scale * kLog2e;
-  const int lane_base = lane & ~(LPT - 1);
-  bool dead = false;
-
-  for (int j = 0; j < nblk; ++j) {
-    const int slot = j % STAGES;
-    const bool ok = wait_bar(attn_smem_u32(&full[pair][slot]), (uint32_t)((j / STAGES) & 1));
-    if (!__all_sync(0xffffffffu, ok)) {
-      if (lane == 0 && p.err_flag) atomicExch(p.err_flag, 7);
-      dead = true;
-      break;
-    }
-    const int lb = lb_begin + pair + j * kPairs;
-    const int t_lo = max(st - lb * BS, 0), t_hi = min(pos - lb * BS, BS - 1);
-    const bool whole = (t_lo == 0) && (t_hi == BS - 1);
-    const float* Kt = ring + (size_t)slot * (kTileBytes / 4);
-    const float* Vt = Kt + BS * HD;
-
-    // ---- A: scores ---------------------------------------------------------------------------------------
-    float sc[STEPS];
-#pragma unroll
-    for (int stp = 0; stp < STEPS; ++stp) {
-      const int t = stp * TPW + tg;
-      const float4 k0 = *reinterpret_cast<const float4*>(Kt + t * HD + li * 4);
-      const float4 k1 = *reinterpret_cast<const float4*>(Kt + t * HD + (li + LPT) * 4);
-      const float2 kk[4] = {make_float2(k0.x, k0.y), make_float2(k0.z, k0.w), make_float2(k1.x, k1.y), make_float2(k1.z, k1.w)};
-      float vals[GW];
-#pragma unroll
-      for (int g = 0; g < GW; ++g) {
-        float2 d = __fmul2_rn(qv[g][0], kk[0]);
-        d = __ffma2_rn(qv[g][1], kk[1], d);
-        d = __ffma2_rn(qv[g][2], kk[2], d);
-        d = __ffma2_rn(qv[g][3], kk[3], d);
-        vals[g] = d.x + d.y;
-      }
-      // reduce-scatter over the LPT lanes of the token: halve the value count per step while it is > 1
-      int n = GW;
-#pragma unroll
-      for (int o = 1; o < LPT; o <<= 1) {
-        if (n > 1) {
-          const int h = n >> 1;
-          const bool up = (lane & o) != 0;
-#pragma unroll
-          for (int i = 0; i < (GW > 1 ? GW / 2 : 1); ++i) {
-            if (i < h) {
-              const float send = up ? vals[i] : vals[i + h];
-              const float recv = __shfl_xor_sync(0xffffffffu, send, o);
-              vals[i] = (up ? vals[i + h] : vals[i]) + recv;
-            }
-          }
-          n = h;
-        } else {
-          vals[0] += __shfl_xor_sync(0xffffffffu, vals[0], o);
-        }
-      }
-      const bool valid = whole || (t >= t_lo && t <= t_hi);
-      sc[stp] = valid ? vals[0] * scale2 : -INFINITY;
-    }
-
-    // ---- B: one softmax update per tile ---------------------------------------------------------------------
-    float tmax = sc[0];
-#pragma unroll
-    for (int stp = 1; stp < STEPS; ++stp) tmax = fmaxf(tmax, sc[stp]);
-#pragma unroll
-    for (int o = LPT; o < 32; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));  // across token groups
-    const float m_new = fmaxf(m_own, tmax);
-    const float corr = (m_own == -INFINITY) ? 1.f : ex2_approx(m_own - m_new);
-    float pr[STEPS];
-    float psum = 0.f;
-#pragma unroll
-    for (int stp = 0; stp < STEPS; ++stp) {
-      pr[stp] = (sc[stp] == -INFINITY) ? 0.f : ex2_approx(sc[stp] - m_new);
-      psum += pr[stp];
-    }
-    l_own = l_own * corr + psum;
-    m_own = m_new;
-
-    // ---- C: accumulate ---------------------------------------------------------------------------------------
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int g = 0; g < GW; ++g) {
-        const float cg_ = __shfl_sync(0xffffffffu, corr, lane_base + attn_owner_lane<GW, LPT>(g));
-        const float2 c2 = make_float2(cg_, cg_);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[g][i] = __fmul2_rn(acc[g][i], c2);
-      }
-    }
-#pragma unroll
-    for (int stp = 0; stp < STEPS; ++stp) {
-      const int t = stp * TPW + tg;
-      float4 v0 = *reinterpret_cast<const float4*>(Vt + t * HD + li * 4);
-      float4 v1 = *reinterpret_cast<const float4*>(Vt + t * HD + (li + LPT) * 4);
-      if (!whole && !(t >= t_lo && t <= t_hi)) {  // never multiply a slot that was not written for this sequence
-        v0 = make_float4(0.f, 0.f, 0.f, 0.f);
-        v1 = v0;
-      }
-      const float2 vv[4] = {make_float2(v0.x, v0.y), make_float2(v0.z, v0.w), make_float2(v1.x, v1.y), make_float2(v1.z, v1.w)};
-#pragma unroll
-      for (int g = 0; g < GW; ++g) {
-        const float pg = __shfl_sync(0xffffffffu, pr[stp], lane_base + attn_owner_lane<GW, LPT>(g));
-        const float2 p2 = make_float2(pg, pg);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[g][i] = __ffma2_rn(p2, vv[i], acc[g][i]);
-      }
-    }
-    __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(attn_smem_u32(&empty[pair][slot])) : "memory");
-    if (issuer && j + STAGES < nblk) {   // both warps of the pair have left the slot: refill it
-      if (wait_bar(attn_smem_u32(&empty[pair][slot]), (uint32_t)((j / STAGES) & 1))) {
-        issue(j + STAGES, pb_next);
-        if (j + 1 + STAGES < nblk) pb_next = lookup(j + 1 + STAGES);
-      } else if (p.err_flag) {
-        atomicExch(p.err_flag, 7);
-      }
-    }
-  }
-  if (dead) {   // bounded drain of the copies that may still be landing in this CTA's shared memory
-    for (int i = 0; i < 200; ++i) __nanosleep(100);
-  }
-
-  // ---- merge the token groups of the warp (the owned head's m, l; every head's accumulator) -------------------
-  float m_all = m_own;
-#pragma unroll
-  for (int o = LPT; o < 32; o <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
-  const float f_own = (m_own == -INFINITY) ? 0.f : ex2_approx(m_own - m_all);
-  float l_all = l_own * f_own;
-#pragma unroll
-  for (int o = LPT; o < 32; o <<= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, o);
-#pragma unroll
-  for (int g = 0; g < GW; ++g) {
-    const float fg = __shfl_sync(0xffffffffu, f_own, lane_base + attn_owner_lane<GW, LPT>(g));
-    const float2 f2 = make_float2(fg, fg);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 a = __fmul2_rn(acc[g][i], f2);
-#pragma unroll
-      for (int o = LPT; o < 32; o <<= 1) {
-        a.x += __shfl_xor_sync(0xffffffffu, a.x, o);
-        a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
-      }
-      acc[g][i] = a;
-    }
-  }
-  __syncthreads();  // every pair is done with its ring: reuse it for the cross-warp exchange
-  float* s_acc = reinterpret_cast<float*>(attn_smem);  // [warps][GW][HD]
-  if (tg == 0) {
-#pragma unroll
-    for (int g = 0; g < GW; ++g) {
-      float* dstp = s_acc + ((size_t)warp * GW + g) * HD;
-      *reinterpret_cast<float4*>(dstp + li * 4) = make_float4(acc[g][0].x, acc[g][0].y, acc[g][1].x, acc[g][1].y);
-      *reinterpret_cast<float4*>(dstp + (li + LPT) * 4) = make_float4(acc[g][2].x, acc[g][2].y, acc[g][3].x, acc[g][3].y);
-    }
-    const int g_own = attn_owned_head<GW, LPT>(li);
-    if (attn_owner_lane<GW, LPT>(g_own) == li) {  // one writer per head
-      s_m[warp][g_own] = m_all;
-      s_l[warp][g_own] = l_all;
-    }
-  }
-  __syncthreads();
-  pi_grid_launch_dependents();
-  constexpr float kLn2 = 0.6931471805599453f;
-  for (int idx = tid; idx < G * HD; idx += kPairWarps * 32) {
-    const int g = idx / HD, d = idx - g * HD;
-    const int h2 = g / GW, gl = g - h2 * GW;        // which warp of a pair holds head g, and where
-    float M = -INFINITY;
-#pragma unroll
-    for (int pr2 = 0; pr2 < kPairs; ++pr2) M = fmaxf(M, s_m[pr2 * 2 + h2][gl]);
-    float ls = 0.f, a = 0.f;
-#pragma unroll
-    for (int pr2 = 0; pr2 < kPairs; ++pr2) {
-      const int w = pr2 * 2 + h2;
-      const float f = (s_m[w][gl] == -INFINITY) ? 0.f : ex2_approx(s_m[w][gl] - M);
-      ls += s_l[w][gl] * f;
-      a += s_acc[((size_t)w * GW + gl) * HD + d] * f;
-    }
-    const int h = kvh * G + g;
-    if (p.nsplit == 1) {
-      p.out[(size_t)b * p.out_stride + (size_t)h * HD + d] = a * (1.0f / fmaxf(ls, 1e-12f));
-    } else {
-      const size_t slot = ((size_t)b * p.H + h) * p.nsplit + split;
-      p.part_acc[slot * HD + d] = a;
-      if (d == 0) {
-        p.part_ml[slot * 2] = M * kLn2;  // the merge kernel works in the natural-log domain
-        p.part_ml[slot * 2 + 1] = ls;
-      }
-    }
-  }
-}
-
 // grid (H, B), HD threads (rounded up to a warp): merge the KV splits.
 __global__ void attn_combine_kernel(const AttnParams p, int HD) {
   pi_grid_dependency_wait();
@@ -1111,37 +833,6 @@ cudaError_t launch_v3(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p, si
   }
 }
 
-template <int HD, int G, int STAGES>
-cudaError_t launch_pair_one(pi_ctx* ctx, dim3 grid, const AttnParams& p, size_t smem) {
-  auto k = attn_decode_pair_kernel<HD, G, STAGES>;
-  static pi_smem_grant granted;
-  if (smem > granted.of(ctx)) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    granted.of(ctx) = smem;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(kPairWarps * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, k, p);
-}
-
-template <int HD, int STAGES>
-cudaError_t launch_pair(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p, size_t smem) {
-  switch (group) {
-    case 2: return launch_pair_one<HD, 2, STAGES>(ctx, grid, p, smem);
-    case 4: return launch_pair_one<HD, 4, STAGES>(ctx, grid, p, smem);
-    default: return launch_pair_one<HD, 8, STAGES>(ctx, grid, p, smem);
-  }
-}
-
 template <int HD, int STAGES>
 cudaError_t launch_tma(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p, size_t smem) {
   switch (group) {
@@ -1281,9 +972,7 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   const size_t tile_bytes = 2 * (size_t)L.block_size * HD * sizeof(float);
   const int stages = HD == 64 ? 3 : 2;
   const size_t ring_bytes = (size_t)kAttnWarps * stages * tile_bytes;
-  if (ctx->opt_attn_tma == 1 && L.block_size == 16 && group >= 2)    // two warps per tile, half the query heads each
-    e = HD == 64 ? launch_pair<64, 3>(ctx, group, grid, p, ring_bytes / 2) : launch_pair<128, 2>(ctx, group, grid, p, ring_bytes / 2);
-  else if ((ctx->opt_attn_tma == 1 || ctx->opt_attn_tma == 3) && L.block_size == 16)   // 3: one warp per tile, all heads
+  if (ctx->opt_attn_tma == 1 && L.block_size == 16)
     e = HD == 64 ? launch_v3<64, 3>(ctx, group, grid, p, ring_bytes) : launch_v3<128, 2>(ctx, group, grid, p, ring_bytes);
   else if (ctx->opt_attn_tma && tile_bytes % 16 == 0 && ring_bytes + 4096 <= ctx->smem_optin && tile_bytes < (1u << 20))
     e = HD == 64 ? launch_tma<64, 3>(ctx, group, grid, p, ring_bytes) : launch_tma<128, 2>(ctx, group, grid, p, ring_bytes);
