@@ -583,7 +583,7 @@ pi_status pi_paged_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int
   PI_TRY(check_tables(ctx, pool, block_tables_host, max_blocks, table_lens_host, B));
   pi_attn_batch batch;
   PI_TRY(pi_upload_attn_batch(ctx, block_tables_host, max_blocks, table_lens_host, pos_host, start_host, B,
-                              pool->L.block_size, &batch));
+                              pool->L.block_size, pool->L.num_blocks, &batch));
   return pi_launch_attention(ctx, pool, layer, num_heads, q_dev, q_stride, out_dev, out_stride, batch);
 }
 

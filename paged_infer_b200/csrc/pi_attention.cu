@@ -43,6 +43,7 @@ struct AttnParams {
   const int32_t* lens;
   const int32_t* pos;
   const int32_t* start;
+  const int32_t* safe_lb;   // [B] or null: blocks below this index may be fetched before the dependency wait
   int blocks_per_cta;
   int nsplit;
   float* part_ml;   // [B][H][nsplit][2]
@@ -451,14 +452,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncwarp();
-  pi_grid_dependency_wait();
 
-  const int pos = p.pos[b], st = p.start[b], len = p.lens[b];
-  const int lb_first = st / BS, lb_last = pos / BS;
-  const int lb_begin = lb_first + split * p.blocks_per_cta;
-  const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);
-  const int nblk = (st <= pos && lb_begin + warp < lb_end) ? (lb_end - lb_begin - warp + kAttnWarps - 1) / kAttnWarps : 0;
-
+  int lb_begin = split * p.blocks_per_cta;   // first logical block of this CTA (an entry without a window start)
   // physical block of this warp's tile j (lane 0 looks it up one tile ahead of the copy that needs it, so the
   // table read is not on the path between two tiles)
   auto lookup = [&](int j) { return p.tables[(size_t)b * p.max_blocks + lb_begin + warp + j * kAttnWarps]; };
@@ -471,9 +466,25 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const A
                  "r"(kTileBytes), "r"(bar)
                  : "memory");
   };
+  // Tiles of blocks that were complete when the batch was uploaded (everything below the entry's position then, for
+  // an entry without a window start) do not depend on the kernel ahead of this one in the stream, and neither do the
+  // block tables: the first copies of the ring go out before the dependency wait.  Such an entry starts at block 0,
+  // so this CTA's range is known without reading the (device-updated) positions.
+  const int len = p.lens[b];
+  const int safe = p.safe_lb ? min(p.safe_lb[b], len) : 0;
+  int npre = 0;
+  if (lane == 0)
+    for (; npre < STAGES && lb_begin + warp + npre * kAttnWarps < min(safe, lb_begin + p.blocks_per_cta); ++npre) issue(npre, lookup(npre));
+  pi_grid_dependency_wait();
+
+  const int pos = p.pos[b], st = p.start[b];
+  const int lb_first = st / BS, lb_last = pos / BS;
+  lb_begin = lb_first + split * p.blocks_per_cta;   // unchanged when anything was fetched early (then st == 0)
+  const int lb_end = min(min(lb_last + 1, lb_begin + p.blocks_per_cta), len);
+  const int nblk = (st <= pos && lb_begin + warp < lb_end) ? (lb_end - lb_begin - warp + kAttnWarps - 1) / kAttnWarps : 0;
   int pb_next = -1;
   if (lane == 0) {
-    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j, lookup(j));
+    for (int j = npre; j < STAGES && j < nblk; ++j) issue(j, lookup(j));
     if (STAGES < nblk) pb_next = lookup(STAGES);
   }
 
@@ -847,18 +858,19 @@ cudaError_t launch_tma(pi_ctx* ctx, int group, dim3 grid, const AttnParams& p, s
 
 // Host block tables and per-entry metadata -> one device buffer, through pinned memory.
 pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
-                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size,
+                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size, int num_blocks,
                                pi_attn_batch* out) {
   PI_REQUIRE(ctx, B > 0, "attention needs at least one entry");
   PI_REQUIRE(ctx, max_blocks >= 0 && block_size > 0, "bad block table shape");
   const int mb = std::max(max_blocks, 1);
-  const size_t n = (size_t)B * mb + 3 * (size_t)B;
+  const size_t n = (size_t)B * mb + 4 * (size_t)B;
   PI_TRY(pi_reserve(ctx, &ctx->attn_tables, n * sizeof(int32_t)));
   PI_TRY(pi_reserve_pinned(ctx, n * sizeof(int32_t)));
   int32_t* h = static_cast<int32_t*>(ctx->pinned);
   int32_t* h_lens = h + (size_t)B * mb;
   int32_t* h_pos = h_lens + B;
   int32_t* h_start = h_pos + B;
+  int32_t* h_safe = h_start + B;
   long total = 0;
   int widest = 0;
   bool shared = B > 1;
@@ -873,10 +885,35 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
     h_lens[b] = len;
     h_pos[b] = pos_host[b];
     h_start[b] = start_host[b];
+    h_safe[b] = 0;
     if (start_host[b] <= pos_host[b]) {
       const int nb = pos_host[b] / block_size - start_host[b] / block_size + 1;
       total += nb;
       widest = std::max(widest, nb);
+    }
+  }
+  // Which leading blocks of an entry may be fetched before the K/V writes of this step have landed: those below its
+  // position that no entry of the batch writes in this step (an entry writes the block that holds its position; several
+  // positions of one sequence in one batch - a prefill chunk, a speculative group - write blocks that the others read).
+  if (num_blocks > 0) {
+    std::vector<uint8_t>& written = ctx->scratch_block_marks;
+    written.assign((size_t)num_blocks, 0);
+    for (int b = 0; b < B; ++b) {
+      const int lb = pos_host[b] / block_size;
+      if (lb < lens_host[b]) {
+        const int32_t pb = tables_host[(size_t)b * max_blocks + lb];
+        if (pb >= 0 && pb < num_blocks) written[pb] = 1;
+      }
+    }
+    for (int b = 0; b < B; ++b) {
+      if (start_host[b] != 0) continue;
+      const int limit = std::min(pos_host[b] / block_size, lens_host[b]);
+      int lb = 0;
+      for (; lb < limit; ++lb) {
+        const int32_t pb = tables_host[(size_t)b * max_blocks + lb];
+        if (pb < 0 || pb >= num_blocks || written[pb]) break;
+      }
+      h_safe[b] = lb;
     }
   }
   int32_t* d = static_cast<int32_t*>(ctx->attn_tables.ptr);
@@ -886,6 +923,7 @@ pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_
   out->lens = d + (size_t)B * mb;
   out->pos = out->lens + B;
   out->start = out->pos + B;
+  out->safe_lb = out->start + B;
   out->B = B;
   out->max_window_blocks = widest;
   out->total_window_blocks = total;
@@ -917,6 +955,7 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
   p.lens = batch.lens;
   p.pos = batch.pos;
   p.start = batch.start;
+  p.safe_lb = batch.safe_lb;
   p.scale = 1.0f / sqrtf((float)HD);
   p.err_flag = ctx->dev_err;
   p.nsplit = 1;

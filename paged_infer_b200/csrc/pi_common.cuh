@@ -99,6 +99,7 @@ struct pi_ctx {
   pi_buffer attn_tables;               // block tables + per-entry (len, pos, start)
   pi_buffer attn_partial;              // split-KV partial (m, l, acc)
   pi_buffer gemm_act;                  // bf16 activation planes (+ row factors) for the tensor GEMM
+  std::vector<uint8_t> scratch_block_marks;   // host: physical blocks written by the step being staged
   void* pinned = nullptr;              // pinned host staging
   size_t pinned_bytes = 0;
 };
@@ -230,6 +231,10 @@ struct pi_attn_batch {
   const int32_t* lens = nullptr;    // device [B]
   const int32_t* pos = nullptr;     // device [B]
   const int32_t* start = nullptr;   // device [B]
+  // device [B]: logical blocks below this index are complete and will not be written by anything queued after the
+  // upload (the position the host passed, in blocks; 0 for an entry with a window start): a kernel may fetch them
+  // before it has waited for the kernel ahead of it.  Never updated on the device.
+  const int32_t* safe_lb = nullptr;
   int B = 0;
   int max_window_blocks = 0;        // host-side bound on blocks any window touches
   long total_window_blocks = 0;     // host-side sum
@@ -237,7 +242,7 @@ struct pi_attn_batch {
   int shared_len = 0;               // ... of this many blocks
 };
 pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
-                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size,
+                               const int32_t* pos_host, const int32_t* start_host, int B, int block_size, int num_blocks,
                                pi_attn_batch* out);
 // `emit` (optional): when the KV axis is split and a merge kernel runs anyway, that kernel also writes the output as
 // bf16 planes (row factor 1) for the projection that follows; *emitted tells whether it did.

@@ -539,7 +539,7 @@ pi_status stage_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t
     }
   }
   PI_TRY(ensure_rope(ctx, m, max_pos + 1));
-  PI_TRY(pi_upload_attn_batch(ctx, tables, max_blocks, lens, positions, start.data(), B, pool->L.block_size, batch));
+  PI_TRY(pi_upload_attn_batch(ctx, tables, max_blocks, lens, positions, start.data(), B, pool->L.block_size, pool->L.num_blocks, batch));
   PI_CUDA(ctx, cudaMemcpyAsync(m->tokens_dev, tokens, B * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream));
   return PI_OK;
 }
