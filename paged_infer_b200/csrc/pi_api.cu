@@ -217,6 +217,7 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_ATTN_TMA: ctx->opt_attn_tma = value; return PI_OK;
     case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
+    case PI_OPT_TP_PUSH: ctx->opt_tp_push = value != 0; return PI_OK;
     case PI_OPT_PEER_SPIN_LIMIT:
       PI_REQUIRE(ctx, value >= 0, "the spin limit cannot be negative");
       ctx->peer_spin_limit = (uint32_t)value;

@@ -76,6 +76,7 @@ struct pi_ctx {
     unsigned long long* flags[8] = {};          // every rank's flag array
     void* mapped[8] = {};                       // what cudaIpcOpenMemHandle returned (to close)
     int next_slot = 0;
+    bool pushed = false;                        // the partial sums of the next exchange were pushed into every rank's buffer
   } peer;
   uint32_t peer_spin_limit = 0;   // polls a rank waits for a peer's partial sums; 0 = the default (about a second)
 
@@ -86,6 +87,7 @@ struct pi_ctx {
   int opt_gemv_max_m = 4;
   int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always, 3 always and on the mma.sync kernel
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
+  bool opt_tp_push = true;  // tensor parallel, peer path: row-split projections push their partial sums into every rank's buffer
   int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 
   // per-kernel-class timing with CUDA events on this stream (off by default)
@@ -182,6 +184,10 @@ struct pi_linear_args {
   const float* emit_norm_weight = nullptr;
   float emit_norm_eps = 0.f;
   const pi_rope_kv* rope = nullptr;
+  // Tensor-core path, plain store epilogue only: the result is also stored at the same offsets under these bases
+  // (peer memory of the other tensor-parallel ranks).
+  float* out_also[8] = {};
+  int n_out_also = 0;
 };
 
 // CUDA-core dequant GEMV/GEMM (any shape, any M).
@@ -292,6 +298,10 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
 // for all ranks' partials of that slot, adds them in rank order and adds the sum to x.
 bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n);
 float* pi_tp_peer_slot(pi_ctx* ctx);
+// Push variant: where the same partial sums go in the other ranks' buffers (tp - 1 pointers into peer memory, written
+// to `out`; returns their number).  The projection stores its result there as well as in pi_tp_peer_slot(); the next
+// pi_tp_peer_reduce_add then reads every rank's partial sums from local memory.
+int pi_tp_peer_push_targets(pi_ctx* ctx, float** out);
 // `emit` (optional): also write the new rows of x as planes (times emit_norm_weight, with the per-chunk sums of
 // squares the consumer turns into 1/rms), so that the projection that follows needs no split kernel.
 pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_act_planes* emit = nullptr,

@@ -527,6 +527,16 @@ pi_status build_gemm_params(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
   p.ksplit = 1;
   p.nkb = nkb;
   p.epi = a.epi;
+  if (a.n_out_also > 0) {
+    PI_REQUIRE(ctx, a.epi == PI_EPI_STORE && !a.emit && !a.rope && N % 4 == 0 && a.out_stride % 4 == 0 && (uintptr_t)a.out % 16 == 0 &&
+                        a.n_out_also <= 8,
+               "extra store targets need a plain store epilogue over whole 16-byte groups");
+    p.n_out_also = a.n_out_also;
+    for (int i = 0; i < a.n_out_also; ++i) {
+      PI_REQUIRE(ctx, a.out_also[i] && (uintptr_t)a.out_also[i] % 16 == 0, "extra store target %d is null or misaligned", i);
+      p.out_also[i] = a.out_also[i];
+    }
+  }
   p.err_flag = ctx->dev_err;
   p.act_scale = in.row_scale;
   p.sumsq_in = in.row_scale ? nullptr : (in.sumsq_tiles > 0 ? in.sumsq : nullptr);

@@ -29,6 +29,8 @@ struct GemmParams {
   int N, K, M;
   int ksplit, nkb;          // K splits, total K blocks
   int epi;
+  int n_out_also;           // plain store epilogue: the result also goes to these bases (other ranks' memory)
+  float* out_also[8];
   int* err_flag;
   // row factor of the activations: given, or derived from partial sums of squares, or 1
   const float* act_scale;   // [M]
@@ -290,6 +292,8 @@ __device__ __forceinline__ void epi_row(const GemmParams& p, const EpiRows& e, i
           r[0] += old.x; r[1] += old.y; r[2] += old.z; r[3] += old.w;
         }
         *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+        for (int i = 0; i < p.n_out_also; ++i)   // tensor-parallel push: posted stores into the peers' buffers
+          *reinterpret_cast<float4*>(p.out_also[i] + (size_t)m * p.out_stride + rr) = make_float4(r[0], r[1], r[2], r[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i)

@@ -398,6 +398,8 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     if (ctx->tp > 1) {
       o.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       o.out_stride = hidden;
+      if (peer && ctx->opt_tp_push && pi_gemm_tc_will_run(ctx, m->wo[l], o) && m->wo[l]->rows % 4 == 0)
+        o.n_out_also = pi_tp_peer_push_targets(ctx, o.out_also);   // the epilogue stores into the peers' buffers too
       PI_TRY(pi_linear_forward(ctx, m->wo[l], o));
       if (peer) {   // the exchange kernel adds the residual and hands the new rows on as planes
         x_ready = g_tc;
@@ -437,6 +439,8 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
       d.out = peer ? pi_tp_peer_slot(ctx) : m->partial;
       d.out_stride = hidden;
       if (h_ready) d.in_planes = &ph;
+      if (peer && ctx->opt_tp_push && pi_gemm_tc_will_run(ctx, m->down[l], d) && m->down[l]->rows % 4 == 0)
+        d.n_out_also = pi_tp_peer_push_targets(ctx, d.out_also);
       PI_TRY(pi_linear_forward(ctx, m->down[l], d));
       if (peer) {
         const pi_linear* next = l + 1 < L ? m->qkv[l + 1] : (final_x ? m->lm_head : nullptr);

@@ -114,10 +114,16 @@ pi_status pi_tp_all_gather(pi_ctx* ctx, const void* send, void* recv, size_t byt
 
 // ---- peer-memory exchange ----------------------------------------------------------------------------------------
 //
-// Layout of every rank's allocation: [slot 0 floats | slot 1 floats | flags[2][8] u64 | epoch[2] u64 | ticket[2] u32].
-// Two slots alternate between consecutive exchanges (o, down, o, ...).  A rank may overwrite slot s again only after
-// the exchange on slot 1-s, and that exchange cannot finish before every peer has started it, i.e. has finished
-// reading slot s: no reader is ever overtaken.
+// Layout of every rank's allocation: [slot 0: tp regions of floats | slot 1: tp regions | flags[2][8] u64 | epoch[2] u64 |
+// ticket[2] u32]; region r of a slot holds rank r's partial sums.  Two ways to fill it:
+//   pull  a rank writes its partial sums into ITS OWN region of its own buffer, and the exchange kernel of every rank
+//         reads region r from rank r's buffer (NVLink P2P loads);
+//   push  the projection that produced the partial sums wrote them into its region of EVERY rank's buffer from its
+//         epilogue (plain peer stores, posted while the rest of the projection is still computing), and the exchange
+//         kernel reads all regions from its own memory.
+// Two slots alternate between consecutive exchanges (o, down, o, ...).  A rank may overwrite slot s again (in its own
+// or, pushing, in its peers' buffers) only after the exchange on slot 1-s, and that exchange cannot finish before every
+// peer has started it, i.e. has finished reading slot s: no reader is ever overtaken.
 namespace {
 constexpr int kPeerSlots = 2;
 constexpr int kPeerMaxTp = 8;
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(256) tp_peer_reduce_add_kernel(const PeerReduc
   }
 }
 
-size_t peer_flags_offset(size_t slot_floats) { return kPeerSlots * slot_floats * sizeof(float); }
+size_t peer_flags_offset(size_t slot_floats, int tp) { return (size_t)kPeerSlots * tp * slot_floats * sizeof(float); }
 }  // namespace
 
 extern "C" pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* handle_out) {
@@ -258,7 +264,7 @@ extern "C" pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* han
   PI_REQUIRE(ctx, !ctx->peer.base, "the peer buffers of this context exist already");
   static_assert(sizeof(cudaIpcMemHandle_t) == PI_TP_PEER_HANDLE_BYTES, "cudaIpcMemHandle_t is 64 bytes");
   const size_t slot_floats = (max_floats + 63) / 64 * 64;
-  const size_t bytes = peer_flags_offset(slot_floats) + (kPeerSlots * kPeerMaxTp + kPeerSlots) * sizeof(unsigned long long) +
+  const size_t bytes = peer_flags_offset(slot_floats, ctx->tp) + (kPeerSlots * kPeerMaxTp + kPeerSlots) * sizeof(unsigned long long) +
                        kPeerSlots * sizeof(unsigned int) + 64;
   PI_CUDA(ctx, cudaMalloc(&ctx->peer.base, bytes));
   PI_CUDA(ctx, cudaMemset(ctx->peer.base, 0, bytes));
@@ -282,7 +288,7 @@ extern "C" pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles) {
       ctx->peer.mapped[r] = base;
     }
     ctx->peer.data[r] = static_cast<float*>(base);
-    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(base) + peer_flags_offset(ctx->peer.slot_floats));
+    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(base) + peer_flags_offset(ctx->peer.slot_floats, ctx->tp));
   }
   ctx->peer.next_slot = 0;
   ctx->peer.ready = true;
@@ -298,7 +304,7 @@ extern "C" pi_status pi_tp_peer_import_pointers(pi_ctx* ctx, void* const* bases)
   for (int r = 0; r < ctx->tp; ++r) {
     PI_REQUIRE(ctx, bases[r] != nullptr, "rank %d has no buffer", r);
     ctx->peer.data[r] = static_cast<float*>(bases[r]);
-    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(bases[r]) + peer_flags_offset(ctx->peer.slot_floats));
+    ctx->peer.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(bases[r]) + peer_flags_offset(ctx->peer.slot_floats, ctx->tp));
   }
   ctx->peer.next_slot = 0;
   ctx->peer.ready = true;
@@ -325,7 +331,20 @@ bool pi_tp_peer_usable(const pi_ctx* ctx, size_t n) {
   return ctx->tp > 1 && ctx->peer.ready && n <= ctx->peer.slot_floats && n % 4 == 0;
 }
 
-float* pi_tp_peer_slot(pi_ctx* ctx) { return ctx->peer.data[ctx->rank] + (size_t)ctx->peer.next_slot * ctx->peer.slot_floats; }
+// Region `region` of the slot of the next exchange in rank `owner`'s buffer.
+static float* peer_region(const pi_ctx* ctx, int owner, int slot, int region) {
+  return ctx->peer.data[owner] + ((size_t)slot * ctx->tp + region) * ctx->peer.slot_floats;
+}
+
+float* pi_tp_peer_slot(pi_ctx* ctx) { return peer_region(ctx, ctx->rank, ctx->peer.next_slot, ctx->rank); }
+
+int pi_tp_peer_push_targets(pi_ctx* ctx, float** out) {
+  int n = 0;
+  for (int r = 0; r < ctx->tp; ++r)
+    if (r != ctx->rank) out[n++] = peer_region(ctx, r, ctx->peer.next_slot, ctx->rank);
+  ctx->peer.pushed = true;   // the next exchange finds every rank's partial sums in its own memory
+  return n;
+}
 
 pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_act_planes* emit, const float* emit_norm_weight,
                                 float emit_norm_eps) {
@@ -341,8 +360,10 @@ pi_status pi_tp_peer_reduce_add(pi_ctx* ctx, float* x, int rows, int cols, pi_ac
   p.tp = ctx->tp;
   p.rank = ctx->rank;
   p.slot = slot;
+  const bool pushed = ctx->peer.pushed;
+  ctx->peer.pushed = false;
   for (int r = 0; r < ctx->tp; ++r) {
-    p.data[r] = ctx->peer.data[r] + (size_t)slot * ctx->peer.slot_floats;
+    p.data[r] = peer_region(ctx, pushed ? ctx->rank : r, slot, r);
     p.flags[r] = ctx->peer.flags[r];
   }
   unsigned long long* epoch = ctx->peer.flags[ctx->rank] + kPeerSlots * kPeerMaxTp;

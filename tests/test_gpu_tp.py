@@ -3,8 +3,11 @@ each rank keeps its shard of the int8 weights and of the KV pool, the row-split
 projections are followed by one NCCL all-reduce, and the logits must agree with
 the single-GPU run of the same model within 1e-4 (only the summation order of the
 partial sums differs) and with the CPU oracle within 1e-3.  The same with the
-exchange done by the library's own kernel over peer memory (NVLink P2P loads,
-arrival flags, residual add folded in) instead of NCCL.  Two geometries: head_dim
+exchange done by the library's own kernels over peer memory instead of NCCL: the
+row-split projection pushes its partial sums into every rank's buffer from its epilogue
+(plain peer stores) and one kernel per exchange waits for the arrival flags and adds
+them up with the residual folded in ("peer-push"), or that kernel fetches the peers'
+partial sums itself with P2P loads ("peer-pull").  Two geometries: head_dim
 64 with kv_group 4, and the Llama-3 / Llama-2-70B one - head_dim 128, kv_group 4,
 ONE KV head per rank.  On a single GPU: a peer that never delivers its partial
 sums makes the bounded wait run out, the call reports PI_ERR_TIMEOUT and the
@@ -44,6 +47,8 @@ def _worker(rank, world, port, out, peer, geom):
         ctx = api.Context(rank, rank=rank, tp=world, nccl_id=ident)
         if peer:
             enable_peer_exchange(ctx, 64 * GEOMETRIES[geom]["hidden"], dist)       # max batch rows x hidden
+            if peer == "pull":   # the exchange kernel fetches the peers' partial sums itself (default: the projections push them)
+                ctx.set_option(api._lib.PI_OPT_TP_PUSH, 0)
         cfg, om, gm = small_llama(ctx, orc, 9, **GEOMETRIES[geom])   # 8 heads / 2 KV heads -> one KV head per rank
         rng = np.random.default_rng(9)
         B, nblocks = 6, 8
@@ -80,7 +85,7 @@ def _worker(rank, world, port, out, peer, geom):
 
 
 @pytest.mark.parametrize("geom", list(GEOMETRIES))
-@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer-memory"])
+@pytest.mark.parametrize("peer", [False, "push", "pull"], ids=["nccl", "peer-push", "peer-pull"])
 def test_tp2_matches_single_gpu_and_oracle(peer, geom):
     import torch
     import torch.multiprocessing as mp
@@ -89,8 +94,8 @@ def test_tp2_matches_single_gpu_and_oracle(peer, geom):
         pytest.skip("needs two GPUs")
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
-    port = 29700 + os.getpid() % 2000 + 2 * list(GEOMETRIES).index(geom)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port + int(peer), out, peer, geom)) for r in range(2)]
+    port = 29700 + os.getpid() % 2000 + 3 * list(GEOMETRIES).index(geom)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port + [False, "push", "pull"].index(peer), out, peer, geom)) for r in range(2)]
     for p in procs:
         p.start()
     res = out.get(timeout=600)
