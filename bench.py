@@ -696,7 +696,10 @@ def tp_decode(args, workload: str, rank: int, world: int, local_rank: int, K: in
             exchange = "nccl all-reduce"
             if not nccl_exchange:
                 enable_peer_exchange(ctx, B * cfg.hidden_size, dist)
-                exchange = "peer memory (P2P loads + flags, residual add folded in)"
+                exchange = "peer memory: partial sums pushed from the projection's epilogue (peer stores), flags, residual add folded in"
+                if args.tp_pull:
+                    ctx.set_option(api._lib.PI_OPT_TP_PUSH, 0)
+                    exchange = "peer memory: partial sums fetched by the exchange kernel (P2P loads), flags, residual add folded in"
         model = api.LlamaWeights.synthetic(ctx, cfg, seed=seed, std=0.02, max_batch=B, max_positions=CTX + K + W + 8)
         kv = api.KvCache(ctx, model.kv_layout(int(first[-1]), BLOCK))
         kv.fill_normal(77 + (rank if tp > 1 else 0), 1.0)
@@ -894,7 +897,8 @@ def main():
     ap.add_argument("--resident-only", action="store_true",
                     help="for a profiler's launch list: only the resident decode leg (warm-up + timed steps) over a pool filled with "
                          "N(0,1) values; prints its step time and exits")
-    ap.add_argument("--nccl-exchange", action="store_true", help="llama3_8b_tp: all-reduce through NCCL instead of the peer-memory kernel")
+    ap.add_argument("--nccl-exchange", action="store_true", help="tensor-parallel workloads: all-reduce through NCCL instead of the peer-memory kernels")
+    ap.add_argument("--tp-pull", action="store_true", help="tensor-parallel workloads: the exchange kernel fetches the peers' partial sums (no push)")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: whatever NCCL logs goes to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
