@@ -407,6 +407,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(local_rank, stream=tstream.cuda_stream)
+    if args.attn_grid:
+        ctx.set_option(api._lib.PI_OPT_ATTN_FLAT, 0)
     model = api.LlamaWeights.synthetic(ctx, cfg, seed=0, std=0.02, max_batch=512, max_positions=4096)
     weight_bytes = model.weight_bytes()
 
@@ -691,6 +693,8 @@ def tp_decode(args, workload: str, rank: int, world: int, local_rank: int, K: in
         tstream = torch.cuda.Stream()
         torch.cuda.set_stream(tstream)
         ctx = api.Context(local_rank, stream=tstream.cuda_stream, rank=rank if tp > 1 else 0, tp=tp, nccl_id=ident)
+        if args.attn_grid:
+            ctx.set_option(api._lib.PI_OPT_ATTN_FLAT, 0)
         exchange = "single GPU"
         if tp > 1:
             exchange = "nccl all-reduce"
@@ -805,6 +809,8 @@ def run_kernel_case(args):
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(0, stream=tstream.cuda_stream)
+    if args.attn_grid:
+        ctx.set_option(api._lib.PI_OPT_ATTN_FLAT, 0)
     rng = np.random.default_rng(11)
     reps = max(args.steps, 1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -841,12 +847,17 @@ def run_kernel_case(args):
         entries = [api.AttnEntry(api.BlockTable(list(range(b * nblk, (b + 1) * nblk))), ctx_len - 1) for b in range(B)]
         attn.run_device(qv, ov, kv, entries)
         torch.cuda.synchronize()
-        e0.record()
+        ctx.profile_begin()                      # device time of the launches only: packing the tables on the host is slow
         for r in range(reps):
             attn.run_device(qv, ov, kv, entries)
-        e1.record()
-        torch.cuda.synchronize()
+        prof = ctx.profile_end()
+        us = prof["attention"][0] * 1e3 / reps   # all launches of one call (work list + kernel, or kernel + merge)
         algo = B * ctx_len * cfg.num_key_value_heads * 2 * cfg.head_dim * 4 + 2 * qv.numel() * 4
+        print(json.dumps({"kernel_case": case, "calls": reps, "us_per_call": round(us, 2), "launches_per_call": prof["attention"][1] / reps,
+                          "algorithmic_bytes": algo, "GB/s": round(algo / us / 1e3, 1),
+                          "frac_of_hbm_peak": round(algo / us / 1e3 / measured_peaks()[0], 3), "peak_kind": f"of {measured_peaks()[2]}"}),
+              flush=True)
+        return
     elif case == "attention_prefill":
         # the last 512-position chunk of a 2048-token prompt: every entry maps the same table
         cfg = LlamaConfig(**TINYLLAMA, quantization="int8")
@@ -898,6 +909,8 @@ def main():
                     help="for a profiler's launch list: only the resident decode leg (warm-up + timed steps) over a pool filled with "
                          "N(0,1) values; prints its step time and exits")
     ap.add_argument("--nccl-exchange", action="store_true", help="tensor-parallel workloads: all-reduce through NCCL instead of the peer-memory kernels")
+    ap.add_argument("--attn-grid", action="store_true",
+                    help="batched decode attention on the per-entry grid (kv head, entry, KV split) instead of the flat tile list")
     ap.add_argument("--tp-pull", action="store_true", help="tensor-parallel workloads: the exchange kernel fetches the peers' partial sums (no push)")
     args = ap.parse_args()
     # stdout carries exactly one JSON line: whatever NCCL logs goes to stderr

@@ -5,7 +5,7 @@ fn main() {
     let out = std::path::PathBuf::from(std::env::var("OUT_DIR").unwrap());
     let src_dir = std::env::var("PAGED_INFER_CUDA_SRC").unwrap_or_else(|_| "../../paged_infer_b200/csrc".into());
     let inc_dir = std::env::var("PAGED_INFER_CUDA_INC").unwrap_or_else(|_| "../../include".into());
-    let srcs = ["pi_api", "pi_attention", "pi_attention_prefill", "pi_attention_prefill_tc", "pi_gemm_tc", "pi_gemv", "pi_glue", "pi_model", "pi_tp"];
+    let srcs = ["pi_api", "pi_attention", "pi_attention_flat", "pi_attention_prefill", "pi_attention_prefill_tc", "pi_gemm_tc", "pi_gemv", "pi_glue", "pi_model", "pi_tp"];
     let mut objs = vec![];
     for s in srcs {
         let o = out.join(format!("{s}.o"));

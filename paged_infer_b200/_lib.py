@@ -26,6 +26,7 @@ PROF_CLASSES = ("gemv", "gemm_tc", "attention", "rope_kv", "other", "collective"
 PI_OPT_TENSOR_GEMM, PI_OPT_CUDA_GRAPH, PI_OPT_PDL, PI_OPT_GEMV_MAX_M, PI_OPT_ATTN_TMA, PI_OPT_FUSE_PLANES, PI_OPT_ATTN_SHARED = 1, 2, 3, 4, 5, 6, 7
 PI_OPT_PEER_SPIN_LIMIT = 8
 PI_OPT_TP_PUSH = 9
+PI_OPT_ATTN_FLAT = 10
 
 
 class PiError(RuntimeError):

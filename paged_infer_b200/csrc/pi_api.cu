@@ -160,7 +160,7 @@ void pi_ctx_destroy(pi_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   pi_tp_destroy(ctx);
-  for (pi_buffer* b : {&ctx->staging_in, &ctx->staging_out, &ctx->attn_tables, &ctx->attn_partial, &ctx->gemm_act})
+  for (pi_buffer* b : {&ctx->staging_in, &ctx->staging_out, &ctx->attn_tables, &ctx->attn_partial, &ctx->attn_plan, &ctx->gemm_act})
     if (b->ptr) cudaFree(b->ptr);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
@@ -218,6 +218,7 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
     case PI_OPT_TP_PUSH: ctx->opt_tp_push = value != 0; return PI_OK;
+    case PI_OPT_ATTN_FLAT: ctx->opt_attn_flat = value != 0; return PI_OK;
     case PI_OPT_PEER_SPIN_LIMIT:
       PI_REQUIRE(ctx, value >= 0, "the spin limit cannot be negative");
       ctx->peer_spin_limit = (uint32_t)value;
@@ -585,6 +586,7 @@ pi_status pi_paged_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int
   pi_attn_batch batch;
   PI_TRY(pi_upload_attn_batch(ctx, block_tables_host, max_blocks, table_lens_host, pos_host, start_host, B,
                               pool->L.block_size, pool->L.num_blocks, &batch));
+  PI_TRY(pi_attention_prepare(ctx, pool, num_heads, batch));
   return pi_launch_attention(ctx, pool, layer, num_heads, q_dev, q_stride, out_dev, out_stride, batch);
 }
 

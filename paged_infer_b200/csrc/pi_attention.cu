@@ -24,6 +24,7 @@
 #include <algorithm>
 
 #include "pi_common.cuh"
+#include "pi_attention.cuh"
 
 namespace {
 
@@ -200,10 +201,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const Attn
 // (TMA, cp.async.bulk) through a per-warp ring of STAGES slots, so several tiles per warp are in
 // flight while one is being consumed.  A lane reads 16-byte chunks `li` and `li + LPT` of a token
 // row, which keeps the 128-bit shared loads free of bank conflicts.
-constexpr uint32_t kAttnSpinLimit = 1u << 21;
-
-__device__ __forceinline__ uint32_t attn_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
 template <int HD, int G, int STAGES>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_tma_kernel(const AttnParams p) {
   constexpr int LPT = HD / 8;    // lanes per token
@@ -398,37 +395,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_tma_kernel(const 
 //   C. accumulation: the probabilities are broadcast back over the token's lanes and multiplied into V with
 //      fma.rn.f32x2; the accumulator is rescaled only when some head's maximum actually moved.
 // Scores are kept in the log2 domain (scale * log2(e) folded into one multiply, ex2.approx for the exponentials).
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// Lane (within the LPT lanes of a token) that ends up owning head g after the reduce-scatter, and back.
-template <int G, int LPT>
-__device__ __forceinline__ constexpr int attn_owner_lane(int g) {
-  int li = 0, n = G, o = 1;
-  while (n > 1 && o < LPT) {
-    n >>= 1;
-    if (g >= n) {
-      li |= o;
-      g -= n;
-    }
-    o <<= 1;
-  }
-  return li;
-}
-template <int G, int LPT>
-__device__ __forceinline__ int attn_owned_head(int li) {
-  int g = 0, n = G, o = 1;
-  while (n > 1 && o < LPT) {
-    n >>= 1;
-    if (li & o) g += n;
-    o <<= 1;
-  }
-  return g;
-}
-
 template <int HD, int G, int STAGES>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_v3_kernel(const AttnParams p) {
   constexpr int BS = 16;
@@ -971,6 +937,8 @@ pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, in
     return pi_launch_attention_shared(ctx, pool, layer, num_heads, q, q_stride, out, out_stride, batch);
   const bool fast = (HD == 64 || HD == 128) && (group == 1 || group == 2 || group == 4 || group == 8) &&
                     ((uintptr_t)q % 16 == 0) && (q_stride % 4 == 0);
+  if (fast && batch.flat_warps > 0 && ((uintptr_t)out % 16 == 0) && (out_stride % 4 == 0))
+    return pi_launch_attention_flat(ctx, pool, layer, num_heads, q, q_stride, out, out_stride, batch, emit, emitted);
   cudaError_t e;
   if (!fast) {
     PI_REQUIRE(ctx, HD <= 32 * kGenericMaxPerLane, "head_dim %d is not supported (max %d)", HD, 32 * kGenericMaxPerLane);

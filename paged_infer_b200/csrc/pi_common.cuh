@@ -87,6 +87,7 @@ struct pi_ctx {
   int opt_gemv_max_m = 4;
   int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always, 3 always and on the mma.sync kernel
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
+  bool opt_attn_flat = true;   // batched decode with many tiles: one equal range of the batch's tile list per resident warp
   bool opt_tp_push = true;  // tensor parallel, peer path: row-split projections push their partial sums into every rank's buffer
   int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 
@@ -100,6 +101,7 @@ struct pi_ctx {
   pi_buffer staging_in, staging_out;   // device copies of host arguments / results
   pi_buffer attn_tables;               // block tables + per-entry (len, pos, start)
   pi_buffer attn_partial;              // split-KV partial (m, l, acc)
+  pi_buffer attn_plan;                 // flat work list of the step: segment ranges, segments, merge info, counters
   pi_buffer gemm_act;                  // bf16 activation planes (+ row factors) for the tensor GEMM
   std::vector<uint8_t> scratch_block_marks;   // host: physical blocks written by the step being staged
   void* pinned = nullptr;              // pinned host staging
@@ -246,6 +248,15 @@ struct pi_attn_batch {
   long total_window_blocks = 0;     // host-side sum
   bool shared_table = false;        // every entry maps the same table row (a prefill chunk, a speculative verify group)
   int shared_len = 0;               // ... of this many blocks
+  // Flat work list of the step (pi_attention_prepare): warp slots it was cut for (0: none, use the per-entry grid),
+  // partial slots, and the device arrays the planning kernel fills.  Set per step, hence mutable.
+  mutable int flat_warps = 0;
+  mutable size_t flat_slots = 0;
+  mutable void* flat_hdr = nullptr;
+  mutable bool flat_settled = false;   // every kernel queued since the planning kernel has waited for its predecessor
+  mutable void* flat_segs = nullptr;
+  mutable void* flat_comb = nullptr;
+  mutable int* flat_counters = nullptr;
 };
 pi_status pi_upload_attn_batch(pi_ctx* ctx, const int32_t* tables_host, int max_blocks, const int32_t* lens_host,
                                const int32_t* pos_host, const int32_t* start_host, int B, int block_size, int num_blocks,
@@ -260,6 +271,10 @@ pi_status pi_launch_attention_shared_tc(pi_ctx* ctx, const pi_kv_pool* pool, int
                                         size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
 pi_status pi_launch_attention_shared(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
                                      size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch);
+pi_status pi_attention_prepare(pi_ctx* ctx, const pi_kv_pool* pool, int num_heads, const pi_attn_batch& batch);
+pi_status pi_launch_attention_flat(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
+                                   size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch,
+                                   pi_act_planes* emit, bool* emitted);
 pi_status pi_launch_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int num_heads, const float* q,
                               size_t q_stride, float* out, size_t out_stride, const pi_attn_batch& batch,
                               pi_act_planes* emit = nullptr, bool* emitted = nullptr);
@@ -350,4 +365,11 @@ __device__ __forceinline__ void pi_grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 __device__ __forceinline__ void pi_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// The other order: nothing queued behind this grid starts before the grid ahead of it has completed.  One such kernel
+// in a chain is a fence for early reads: whatever ran before it is complete in the eyes of EVERY later kernel, even in
+// the part of a later kernel that precedes its own dependency wait.
+__device__ __forceinline__ void pi_grid_dependency_wait_strict() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 #endif

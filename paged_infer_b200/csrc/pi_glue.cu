@@ -16,7 +16,9 @@ namespace {
 
 __global__ void embed_kernel(const uint16_t* __restrict__ table, int vocab, int hidden,
                              const uint32_t* __restrict__ tokens, float* __restrict__ x) {
-  pi_grid_dependency_wait();
+  // strict: the step's attention work list (built by the kernel ahead of this one) is complete before any later kernel
+  // of the step starts, so the attention kernels of layers > 0 may read it ahead of their own dependency wait
+  pi_grid_dependency_wait_strict();
   const int b = blockIdx.x;
   const size_t token = (size_t)(tokens[b] % (uint32_t)vocab);
   const uint16_t* src = table + token * hidden;

@@ -344,6 +344,7 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
   bool x_ready = false;                // px holds the planes of m->x for the next norm
   if (final_x) final_x->valid = false;
 
+  PI_TRY(pi_attention_prepare(ctx, pool, m->heads_local, batch));   // the step's work list, from the positions on the device
   PI_TRY(pi_launch_embed(ctx, m->embed, c.vocab_size, hidden, m->tokens_dev, B, m->x));
   for (int l = 0; l < L; ++l) {
     pi_linear_args a;
@@ -379,6 +380,7 @@ pi_status run_layers(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const pi_attn_b
     o.x_stride = qrows;
     bool a_ready = false;              // the merge kernel of the attention wrote the output as planes too
     const bool o_tc = fuse && m->planes_a && pi_gemm_tc_will_run(ctx, m->wo[l], o);
+    batch.flat_settled = l > 0;   // the work list of the step was complete long before the kernel ahead of this launch started
     PI_TRY(pi_launch_attention(ctx, pool, l, m->heads_local, m->qkv_buf, qkv_stride, m->attn_out, qrows, batch,
                                o_tc ? &pa : nullptr, &a_ready));
     if (a_ready) o.in_planes = &pa;

@@ -120,6 +120,41 @@ def test_long_contexts_split_the_kv_axis(ctx, oracle):
     close(got, cpu_run(oracle, case, q, case.tables, pos, [1500, 0, 299]))
 
 
+@pytest.mark.parametrize("hd,H,KH,batch,blocks", [(64, 32, 4, 40, 100), (128, 32, 8, 12, 80), (128, 8, 1, 64, 100)])
+def test_flat_work_list_ragged_batch(ctx, oracle, hd, H, KH, batch, blocks):
+    """Batches with enough tiles go over the flat tile list (equal ranges per resident warp, partial results merged
+    by the warp that finishes an entry last): ragged positions, windows, an empty window, an empty table, a table
+    that ends before the position.  Same results as the oracle, the same bits run after run, and the per-entry grid
+    (option off) agrees to rounding."""
+    from paged_infer_b200 import _lib
+    bs = 16
+    rng = np.random.default_rng(hd * 7 + H)
+    case = AttnCase(H, KH, hd, bs, batch, blocks, blocks)
+    case.kv_cache = normal_f32(case.kv_cache.size, 21, 1.0)
+    q = normal_f32(batch * H * hd, 22, 1.0)
+    pos = [int(p) for p in rng.integers(bs * blocks // 4, bs * blocks, batch)]
+    st = [0] * batch
+    tables = [list(t) for t in case.tables]
+    pos[0], pos[1], pos[2] = 0, bs * blocks - 1, bs * 7 + 15
+    st[3] = pos[3] - 37                      # sliding window inside the context
+    st[4] = pos[4] + 1                       # empty window
+    tables[5] = []                           # nothing mapped
+    tables[6] = tables[6][:pos[6] // bs // 2]   # the table ends long before the position
+    st[7] = (pos[7] // bs) * bs              # window starts on the position's own block
+    want = cpu_run(oracle, case, q, tables, pos, st)
+    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 1)
+    got = gpu_run(ctx, case, q, tables, pos, st)
+    again = gpu_run(ctx, case, q, tables, pos, st)
+    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 0)
+    grid = gpu_run(ctx, case, q, tables, pos, st)
+    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 1)
+    close(got, want)
+    close(grid, want)
+    assert np.array_equal(got, again)
+    assert np.all(got[4] == 0.0) and np.all(got[5] == 0.0)
+    assert not np.array_equal(got, grid), "the flat work list was not used"
+
+
 def test_kv_pool_roundtrip_copy_block_and_token_io(ctx, oracle):
     from paged_infer_b200 import api
     for (nl, nb, bs, kh, hd) in [(3, 5, 16, 4, 64), (2, 4, 8, 2, 24), (1, 3, 1, 1, 1)]:
