@@ -41,6 +41,13 @@ pi_prof_scope::~pi_prof_scope() {
   if (slot >= 0) cudaEventRecord(ctx->prof_events[2 * slot + 1], ctx->stream);
 }
 
+pi_status pi_enter(pi_ctx* ctx) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev == ctx->device) return PI_OK;
+  PI_CUDA(ctx, cudaSetDevice(ctx->device));
+  return PI_OK;
+}
+
 pi_status pi_reserve(pi_ctx* ctx, pi_buffer* buf, size_t bytes) {
   if (bytes <= buf->bytes) return PI_OK;
   // The old allocation may still be in use by queued kernels.
@@ -70,11 +77,17 @@ pi_status pi_reserve_pinned(pi_ctx* ctx, size_t bytes) {
 }
 
 static pi_status check_device_flag(pi_ctx* ctx) {
-  int flag = 0;
-  PI_CUDA(ctx, cudaMemcpyAsync(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  // word 0: the code of the kernel that gave up; words 1..: that kernel's own record of what it saw (first reporter only)
+  int rec[PI_DEV_ERR_WORDS] = {};
+  PI_CUDA(ctx, cudaMemcpyAsync(rec, ctx->dev_err, sizeof(rec), cudaMemcpyDeviceToHost, ctx->stream));
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  const int flag = rec[0];
   if (flag != 0) {
-    PI_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    PI_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(rec), ctx->stream));
+    if (flag >= 11 && flag <= 13)
+      return pi_fail(ctx, PI_ERR_CUDA, "the attention work list of the step is inconsistent (code %d: warp slot %d, segments %d..%d, "
+                                      "entry %d, kv head %d, blocks %d..%d, physical block %d, item %d); nothing was read through it",
+                     flag, rec[2], rec[3], rec[4], rec[5], rec[6], rec[7], rec[8], rec[9], rec[10]);
     if (flag == 9) {
       // a peer never delivered its partial sums: the slots of the ranks are out of step from here on, so the
       // peer-memory exchange is retired and later steps go through NCCL (or fail loudly without a communicator)
@@ -125,8 +138,8 @@ static pi_status ctx_create_common(int device, void* stream, pi_ctx** out) {
     }
     ctx->own_stream = true;
   }
-  e = cudaMalloc(&ctx->dev_err, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, sizeof(int));
+  e = cudaMalloc(&ctx->dev_err, PI_DEV_ERR_WORDS * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->dev_err, 0, PI_DEV_ERR_WORDS * sizeof(int));
   if (e != cudaSuccess) {
     delete ctx;
     return pi_fail(nullptr, PI_ERR_CUDA, "context allocation: %s", cudaGetErrorString(e));
@@ -170,7 +183,7 @@ void pi_ctx_destroy(pi_ctx* ctx) {
 }
 
 pi_status pi_ctx_synchronize(pi_ctx* ctx) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return check_device_flag(ctx);
 }
@@ -181,7 +194,7 @@ void pi_ctx_reset_kernel_launches(pi_ctx* ctx) {
 }
 
 pi_status pi_ctx_profile_begin(pi_ctx* ctx) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   ctx->prof_on = true;
   ctx->prof_used = 0;
@@ -190,7 +203,7 @@ pi_status pi_ctx_profile_begin(pi_ctx* ctx) {
 }
 
 pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out, uint64_t* launches_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, ms_out && launches_out, "null pointer");
   ctx->prof_on = false;
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -209,7 +222,7 @@ pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out, uint64_t* launches_out
 }
 
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   switch (option) {
     case PI_OPT_TENSOR_GEMM: ctx->opt_tensor_gemm = value != 0; return PI_OK;
     case PI_OPT_CUDA_GRAPH: ctx->opt_graph = value != 0; return PI_OK;
@@ -235,14 +248,14 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
 
 pi_status pi_quantize_rows_i8_dev(pi_ctx* ctx, const float* w_dev, size_t rows, size_t cols, int8_t* q_dev_out,
                                   float* scales_dev_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, w_dev && q_dev_out && scales_dev_out, "null pointer");
   return pi_launch_quantize(ctx, w_dev, cols, rows, cols, q_dev_out, cols, scales_dev_out);
 }
 
 pi_status pi_quantize_rows_i8(pi_ctx* ctx, const float* w_host, size_t rows, size_t cols, int8_t* q_host_out,
                               float* scales_host_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, w_host && q_host_out && scales_host_out, "null pointer");
   if (rows == 0 || cols == 0) {
     for (size_t r = 0; r < rows; ++r) scales_host_out[r] = 1.0f;
@@ -324,7 +337,7 @@ extern "C" {
 
 pi_status pi_linear_create_i8(pi_ctx* ctx, size_t rows, size_t cols, const int8_t* q_host, const float* scales_host,
                               pi_split split, pi_linear** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, q_host && scales_host, "null pointer");
   PI_TRY(pi_linear_alloc(ctx, PI_INT8, rows, cols, split, out));
   pi_linear* lin = *out;
@@ -345,7 +358,7 @@ pi_status pi_linear_create_i8(pi_ctx* ctx, size_t rows, size_t cols, const int8_
 
 pi_status pi_linear_create_quantized(pi_ctx* ctx, size_t rows, size_t cols, const float* w_host, pi_split split,
                                      pi_linear** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, w_host, "null pointer");
   PI_TRY(pi_linear_alloc(ctx, PI_INT8, rows, cols, split, out));
   pi_linear* lin = *out;
@@ -378,7 +391,7 @@ pi_status pi_linear_create_quantized(pi_ctx* ctx, size_t rows, size_t cols, cons
 
 static pi_status create_plain(pi_ctx* ctx, int kind, size_t rows, size_t cols, const void* host, pi_split split,
                               pi_linear** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, host, "null pointer");
   PI_TRY(pi_linear_alloc(ctx, kind, rows, cols, split, out));
   pi_status s = pi_linear_fill(ctx, *out, host, cols, false);
@@ -415,7 +428,7 @@ size_t pi_linear_weight_bytes(const pi_linear* lin) {
 }
 
 pi_status pi_linear_read_i8(pi_ctx* ctx, const pi_linear* lin, int8_t* q_host_out, float* scales_host_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, lin && lin->kind == PI_INT8, "not an int8 projection");
   if (q_host_out)
     PI_CUDA(ctx, cudaMemcpy2DAsync(q_host_out, lin->cols, lin->w, lin->ld, lin->cols, lin->rows, cudaMemcpyDeviceToHost, ctx->stream));
@@ -435,7 +448,7 @@ pi_status pi_linear_forward(pi_ctx* ctx, const pi_linear* lin, const pi_linear_a
 extern "C" {
 
 pi_status pi_linear_apply(pi_ctx* ctx, const pi_linear* lin, const float* x_dev, float* out_dev, int M) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, lin && x_dev && out_dev, "null pointer");
   PI_REQUIRE(ctx, M >= 1, "batch must be at least 1, got %d", M);
   pi_linear_args a;
@@ -448,7 +461,7 @@ pi_status pi_linear_apply(pi_ctx* ctx, const pi_linear* lin, const float* x_dev,
 }
 
 pi_status pi_linear_apply_host(pi_ctx* ctx, const pi_linear* lin, const float* x_host, float* out_host, int M) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, lin && x_host && out_host, "null pointer");
   PI_REQUIRE(ctx, M >= 1, "batch must be at least 1, got %d", M);
   const size_t xin = (size_t)M * lin->cols * sizeof(float), xout = (size_t)M * lin->rows * sizeof(float);
@@ -463,7 +476,7 @@ pi_status pi_linear_apply_host(pi_ctx* ctx, const pi_linear* lin, const float* x
 // ---- KV pool ---------------------------------------------------------------------------------
 
 pi_status pi_kv_pool_create(pi_ctx* ctx, const pi_kv_layout* layout, pi_kv_pool** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, layout && out, "null pointer");
   *out = nullptr;
   PI_REQUIRE(ctx, layout->num_layers > 0 && layout->num_blocks > 0 && layout->block_size > 0 &&
@@ -491,7 +504,7 @@ void pi_kv_pool_destroy(pi_kv_pool* pool) {
 size_t pi_kv_pool_bytes(const pi_kv_pool* pool) { return pool ? pool->floats * sizeof(float) : 0; }
 
 pi_status pi_kv_copy_block(pi_ctx* ctx, pi_kv_pool* pool, int32_t src, int32_t dst) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool, "null pool");
   PI_REQUIRE(ctx, src != dst, "copy_block called with src == dst");
   PI_REQUIRE(ctx, src >= 0 && src < pool->L.num_blocks && dst >= 0 && dst < pool->L.num_blocks,
@@ -500,7 +513,7 @@ pi_status pi_kv_copy_block(pi_ctx* ctx, pi_kv_pool* pool, int32_t src, int32_t d
 }
 
 pi_status pi_kv_fill_normal(pi_ctx* ctx, pi_kv_pool* pool, uint64_t seed, float std) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool, "null pool");
   PI_TRY(pi_launch_fill_normal(ctx, pool->data, pool->floats, seed, 0xCAC4Eull, 0, std));
   PI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -508,7 +521,7 @@ pi_status pi_kv_fill_normal(pi_ctx* ctx, pi_kv_pool* pool, uint64_t seed, float 
 }
 
 pi_status pi_kv_upload(pi_ctx* ctx, pi_kv_pool* pool, const float* cache_host) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool && cache_host, "null pointer");
   PI_TRY(pi_reserve(ctx, &ctx->staging_in, pool->floats * sizeof(float)));
   PI_CUDA(ctx, cudaMemcpyAsync(ctx->staging_in.ptr, cache_host, pool->floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
@@ -518,7 +531,7 @@ pi_status pi_kv_upload(pi_ctx* ctx, pi_kv_pool* pool, const float* cache_host) {
 }
 
 pi_status pi_kv_download(pi_ctx* ctx, const pi_kv_pool* pool, float* cache_host_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool && cache_host_out, "null pointer");
   PI_TRY(pi_reserve(ctx, &ctx->staging_out, pool->floats * sizeof(float)));
   PI_TRY(pi_launch_kv_relayout(ctx, pool, static_cast<float*>(ctx->staging_out.ptr), true));
@@ -551,12 +564,12 @@ static pi_status kv_token_io(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int
 
 pi_status pi_kv_write_token(pi_ctx* ctx, pi_kv_pool* pool, int layer, int32_t block, int tok, const float* k_host,
                             const float* v_host) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   return kv_token_io(ctx, pool, layer, block, tok, const_cast<float*>(k_host), const_cast<float*>(v_host), true);
 }
 pi_status pi_kv_read_token(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int32_t block, int tok, float* k_host_out,
                            float* v_host_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   return kv_token_io(ctx, pool, layer, block, tok, k_host_out, v_host_out, false);
 }
 
@@ -577,7 +590,7 @@ pi_status pi_paged_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int
                              size_t q_stride, float* out_dev, size_t out_stride, const int32_t* block_tables_host,
                              int max_blocks, const int32_t* table_lens_host, const int32_t* pos_host,
                              const int32_t* start_host, int B) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool && q_dev && out_dev && table_lens_host && pos_host && start_host, "null pointer");
   PI_REQUIRE(ctx, block_tables_host || max_blocks == 0, "null block tables");
   if (B == 0) return PI_OK;
@@ -594,7 +607,7 @@ pi_status pi_paged_attention_host(pi_ctx* ctx, const pi_kv_pool* pool, int layer
                                   float* out_host, const int32_t* block_tables_host, int max_blocks,
                                   const int32_t* table_lens_host, const int32_t* pos_host, const int32_t* start_host,
                                   int B) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, pool && q_host && out_host, "null pointer");
   if (B == 0) return PI_OK;
   PI_REQUIRE(ctx, B > 0 && num_heads > 0, "bad batch / head count");
@@ -612,7 +625,7 @@ pi_status pi_paged_attention_host(pi_ctx* ctx, const pi_kv_pool* pool, int layer
 // ---- glue with host buffers --------------------------------------------------------------------------
 
 pi_status pi_rms_norm_host(pi_ctx* ctx, float* x_host_inout, const float* weight_host, int rows, int n, float eps) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, x_host_inout && weight_host && rows >= 0 && n > 0, "bad arguments");
   if (rows == 0) return PI_OK;
   const size_t xb = (size_t)rows * n * sizeof(float), wb = (size_t)n * sizeof(float);
@@ -628,7 +641,7 @@ pi_status pi_rms_norm_host(pi_ctx* ctx, float* x_host_inout, const float* weight
 
 pi_status pi_rope_host(pi_ctx* ctx, float* x_host_inout, const int32_t* pos_host, int rows, int heads, int head_dim,
                        float theta, int style) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, x_host_inout && pos_host && rows >= 0 && heads > 0 && head_dim > 0, "bad arguments");
   PI_REQUIRE(ctx, style == 0 || style == 1, "rope style must be 0 (NeoX) or 1 (interleaved)");
   if (rows == 0) return PI_OK;
@@ -655,7 +668,7 @@ pi_status pi_rope_host(pi_ctx* ctx, float* x_host_inout, const int32_t* pos_host
 }
 
 pi_status pi_swiglu_host(pi_ctx* ctx, float* gate_host_inout, const float* up_host, size_t n) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, gate_host_inout && up_host, "null pointer");
   if (n == 0) return PI_OK;
   PI_TRY(pi_reserve(ctx, &ctx->staging_in, 2 * n * sizeof(float)));
@@ -668,7 +681,7 @@ pi_status pi_swiglu_host(pi_ctx* ctx, float* gate_host_inout, const float* up_ho
 }
 
 pi_status pi_argmax_host(pi_ctx* ctx, const float* logits_host, int rows, int n, uint32_t* out_host) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, logits_host && out_host && rows >= 0 && n > 0, "bad arguments");
   if (rows == 0) return PI_OK;
   const size_t lb = (size_t)rows * n * sizeof(float);

@@ -1,15 +1,17 @@
 // Paged-attention decode over a flat work list (block size 16, head_dim 64 / 128).
 //
-// A batch of ragged windows is a list of K|V tiles: (entry, kv head, logical block).  One launch of the per-entry
+// A batch of ragged windows is a list of K|V tiles: (entry, logical block, kv head).  One launch of the per-entry
 // kernel gives every (kv head, entry, KV split) its own short-lived CTA, so short windows leave CTAs nearly empty,
 // long ones set the tail, and every warp pays the latency of its first tiles for a handful of tiles of work.
-// Here the tiles of the whole batch are laid end to end - entry-major, then kv head, then block - and cut into one
-// equal range per resident warp:
+// Here the blocks of the whole batch are laid end to end - entry after entry - and cut into one equal range per
+// GROUP of num_kv_heads resident warps; the warps of a group walk the same blocks, one kv head each, so the tiles
+// they fetch at about the same time are adjacent in the pool:
 //
 //   attn_plan_kernel   one CTA, once per step (the positions live on the device and move with every step): window
-//                      sizes -> prefix sums -> for every warp slot the SEGMENTS of its range (a segment is the part
-//                      of one (entry, kv head) that falls into the range), and for every (entry, kv head) where its
-//                      partial results will be and how many there are.
+//                      sizes -> prefix sums -> for every group the SEGMENTS of its range (a segment is the part of
+//                      one entry's window that falls into the range), for every warp slot a 64-byte start record
+//                      (its segments, the first one's blocks and physical blocks), and for every (entry, kv head)
+//                      where its partial results will be and how many there are.
 //   attn_decode_flat_kernel   a persistent grid (as many CTAs as fit the GPU at once).  A warp streams the items of its
 //                      range - the query rows of a segment, then its K|V tiles - through one ring of bulk copies that
 //                      never drains between segments.  The arithmetic per tile is that of attn_decode_v3_kernel.  A
@@ -17,6 +19,9 @@
 //                      (m, l, acc) and counts itself in, and the warp that completes the count merges the partials in
 //                      slot order - so the sum does not depend on which warp came last - and writes the output (and,
 //                      on request, its three bf16 planes for the projection that follows).  No merge launch.
+//                      A warp checks what it reads from the work list (segment counts, entry, block range, physical
+//                      block) before it reads anything THROUGH it; an inconsistent list ends the step with an error
+//                      that names what was found, not with a wild address.
 //
 // Replaces PagedAttention::run / for_each_block (reference src/attention.rs:141-295) for batched decode.
 #include <algorithm>
@@ -42,8 +47,8 @@ struct PlanParams {
   int max_blocks;
   int B, KVH, BS, W;
   int4* hdr;       // [W][4]: everything a warp needs to start its copies, in one 64-byte record (see FlatHeader)
-  int4* segs;      // two per segment: {entry, kv head, first block, end block}, {position, window start, -, -}
-  int2* comb;      // [B * KVH]: {first partial slot, number of partials}
+  int4* segs;      // two per group segment: {entry, -, first block, end block}, {position, window start, -, -}
+  int2* comb;      // [B * KVH]: {first group segment, number of group segments}; partial slot = segment * KVH + kv head
   int* counters;   // [B * KVH]
 };
 
@@ -83,31 +88,32 @@ __device__ __forceinline__ int plan_scan_inclusive(int v, int* wt) {
   return v + (warp > 0 ? wt[warp - 1] : 0);
 }
 
-// Segments of warp slot w: counted, or (EMIT) written from slot `seg_base` on.
+// Segments of warp group g (the KVH warps that walk one range of blocks, one kv head each): counted, or (EMIT)
+// written from group-segment `seg_base` on.
 template <bool EMIT>
-__device__ int plan_walk(const PlanParams& pp, const PlanShared& s, int r, long T, int w, int seg_base) {
-  long t = (long)w * r;
+__device__ int plan_walk(const PlanParams& pp, const PlanShared& s, int r, long T, int g, int seg_base) {
+  long t = (long)g * r;
   if (t >= T) return 0;
   const long t1 = min(T, t + (long)r);
-  // the entry that holds tile t: the first i in [1, B] with KVH * P[i] > t, minus one (P[B] * KVH = T > t)
+  // the entry that holds block t of the list: the first i in [1, B] with P[i] > t, minus one (P[B] = T > t)
   int lo = 1, hi = pp.B;
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
-    if ((long)pp.KVH * s.P[mid] > t) hi = mid; else lo = mid + 1;
+    if ((long)s.P[mid] > t) hi = mid; else lo = mid + 1;
   }
   int b = lo - 1, nb = s.n[b];
-  const int rem = (int)(t - (long)pp.KVH * s.P[b]);
-  int kvh = rem / nb, lbr = rem - kvh * nb;
+  int lbr = (int)(t - (long)s.P[b]);
   int cnt = 0;
   while (t < t1) {
     const int take = (int)min((long)(nb - lbr), t1 - t);
     if (EMIT) {
-      const int slot = seg_base + cnt, lb0 = s.first[b] + lbr;
-      pp.segs[2 * slot] = make_int4(b, kvh, lb0, lb0 + take);
-      pp.segs[2 * slot + 1] = make_int4(s.pos[b], s.st[b], 0, 0);
-      if (lbr == 0) {   // the segment that opens this (entry, kv head): its partials are the slots from here on
-        const long off = (long)pp.KVH * s.P[b] + (long)kvh * nb;
-        pp.comb[b * pp.KVH + kvh] = make_int2(slot, (int)((off + nb - 1) / r - off / r + 1));
+      const int j = seg_base + cnt, lb0 = s.first[b] + lbr;
+      pp.segs[2 * j] = make_int4(b, 0, lb0, lb0 + take);
+      pp.segs[2 * j + 1] = make_int4(s.pos[b], s.st[b], 0, 0);
+      if (lbr == 0) {   // the segment that opens this entry: its partials are the group segments from here on
+        const long off = (long)s.P[b];
+        const int2 c = make_int2(j, (int)((off + nb - 1) / r - off / r + 1));
+        for (int kvh = 0; kvh < pp.KVH; ++kvh) pp.comb[b * pp.KVH + kvh] = c;
       }
     }
     ++cnt;
@@ -115,11 +121,8 @@ __device__ int plan_walk(const PlanParams& pp, const PlanShared& s, int r, long 
     lbr += take;
     if (lbr == nb) {
       lbr = 0;
-      if (++kvh == pp.KVH) {
-        kvh = 0;
-        do ++b; while (b < pp.B && s.n[b] == 0);
-        nb = b < pp.B ? s.n[b] : 1;
-      }
+      do ++b; while (b < pp.B && s.n[b] == 0);
+      nb = b < pp.B ? s.n[b] : 1;
     }
   }
   return cnt;
@@ -149,36 +152,46 @@ __global__ void __launch_bounds__(kPlanThreads) attn_plan_kernel(const PlanParam
     pp.counters[pr] = 0;
   }
   __syncthreads();
-  const long T = (long)pp.KVH * s.P[kPlanMaxB];
-  const int r = (int)max((T + pp.W - 1) / pp.W, (long)kMinTilesPerWarp);
-  // two warp slots per thread, consecutive, so that one scan value per thread orders all segments
-  const int w0 = 2 * tid, w1 = 2 * tid + 1;
-  const int c0 = w0 < pp.W ? plan_walk<false>(pp, s, r, T, w0, 0) : 0;
-  const int c1 = w1 < pp.W ? plan_walk<false>(pp, s, r, T, w1, 0) : 0;
+  // The list is cut over GROUPS of KVH warp slots: the warps of a group walk the same blocks, one kv head each, so
+  // the K|V tiles they fetch at about the same time are the adjacent tiles of one physical block.
+  const int NG = pp.W / pp.KVH;
+  const long T = (long)s.P[kPlanMaxB];
+  const int r = (int)max((T + NG - 1) / NG, (long)kMinTilesPerWarp);
+  // two groups per thread, consecutive, so that one scan value per thread orders all segments
+  const int g0 = 2 * tid, g1 = 2 * tid + 1;
+  const int c0 = g0 < NG ? plan_walk<false>(pp, s, r, T, g0, 0) : 0;
+  const int c1 = g1 < NG ? plan_walk<false>(pp, s, r, T, g1, 0) : 0;
   const int inc = plan_scan_inclusive(c0 + c1, s.wt);
   const int base0 = inc - c0 - c1, base1 = base0 + c0;
-  if (c0) plan_walk<true>(pp, s, r, T, w0, base0);
-  if (c1) plan_walk<true>(pp, s, r, T, w1, base1);
-  // the start record of every warp slot (this thread wrote the segments it copies from)
+  if (c0) plan_walk<true>(pp, s, r, T, g0, base0);
+  if (c1) plan_walk<true>(pp, s, r, T, g1, base1);
+  // the start records of the group's warp slots (this thread wrote the segments it copies from)
   for (int k = 0; k < 2; ++k) {
-    const int w = k ? w1 : w0, c = k ? c1 : c0, base = k ? base1 : base0;
-    if (w >= pp.W) continue;
+    const int g = k ? g1 : g0, c = k ? c1 : c0, base = k ? base1 : base0;
+    if (g >= NG) continue;
     int4 a = make_int4(0, 0, 0, 0), bq = a, pbs = make_int4(-1, -1, -1, 0);
     int safe = 0;
     if (c) {
       a = pp.segs[2 * base];
       bq = pp.segs[2 * base + 1];
-      const int32_t* row = pp.tables + (size_t)a.x * pp.max_blocks;
-      pbs.x = row[a.z];
-      if (a.z + 1 < a.w) pbs.y = row[a.z + 1];
-      if (a.z + 2 < a.w) pbs.z = row[a.z + 2];
-      if (pp.safe_lb) safe = pp.safe_lb[a.x];
+      if ((unsigned)a.x < (unsigned)pp.B && a.z >= 0 && a.z < a.w && a.w <= pp.max_blocks) {
+        const int32_t* row = pp.tables + (size_t)a.x * pp.max_blocks;
+        pbs.x = row[a.z];
+        if (a.z + 1 < a.w) pbs.y = row[a.z + 1];
+        if (a.z + 2 < a.w) pbs.z = row[a.z + 2];
+        if (pp.safe_lb) safe = pp.safe_lb[a.x];
+      }
     }
-    pp.hdr[kHdrWords * w + 0] = make_int4(base, base + c, safe, 0);
-    pp.hdr[kHdrWords * w + 1] = a;
-    pp.hdr[kHdrWords * w + 2] = bq;
-    pp.hdr[kHdrWords * w + 3] = pbs;
+    for (int kvh = 0; kvh < pp.KVH; ++kvh) {
+      const int w = g * pp.KVH + kvh;
+      pp.hdr[kHdrWords * w + 0] = make_int4(base, base + c, safe, 0);
+      pp.hdr[kHdrWords * w + 1] = make_int4(a.x, kvh, a.z, a.w);
+      pp.hdr[kHdrWords * w + 2] = bq;
+      pp.hdr[kHdrWords * w + 3] = pbs;
+    }
   }
+  // warp slots past the last whole group (W not a multiple of KVH) have nothing to do
+  for (int w = NG * pp.KVH + tid; w < pp.W; w += kPlanThreads) pp.hdr[kHdrWords * w] = make_int4(0, 0, 0, 0);
 }
 
 struct FlatParams {
@@ -197,6 +210,7 @@ struct FlatParams {
   const int2* comb;
   int* counters;
   int plan_settled;  // the work list was complete before the kernel ahead of this one started: it may be read early
+  int max_slots;     // segments (= partial slots) the work list has room for
   float* part_acc;   // [slot][G][HD]
   float* part_ml;    // [slot][G][2]   (running max in the log2 domain, sum)
   float scale;
@@ -205,6 +219,19 @@ struct FlatParams {
   size_t emit_plane_stride;
   int emit_k;
 };
+
+// A warp that finds its part of the work list inconsistent (a segment count, an entry, a block range or a physical
+// block outside the batch) reads nothing through it: it records what it saw once, raises the error word and stops.
+__device__ __noinline__ void flat_report(int* err, int code, int wslot, int s0, int s1, int4 seg, int pb, int item) {
+  if (!err) return;
+  if (atomicCAS(err + 1, 0, code) == 0) {
+    err[2] = wslot; err[3] = s0; err[4] = s1;
+    err[5] = seg.x; err[6] = seg.y; err[7] = seg.z; err[8] = seg.w;
+    err[9] = pb; err[10] = item;
+    __threadfence();
+  }
+  atomicExch(err, code);
+}
 
 // Four consecutive outputs of (entry b, head h) from dim d: the f32 row and, on request, its planes.
 __device__ __forceinline__ void flat_store4(const FlatParams& p, int b, int h, int HD, int d, float4 v) {
@@ -241,6 +268,7 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
   const int tg = lane / LPT, li = lane % LPT;
   const int wslot = blockIdx.x * kFlatWarps + warp, W = gridDim.x * kFlatWarps;
   const int KVH = p.L.num_kv_heads;
+  const int my_kvh = wslot % KVH;   // the warps of a group walk the same blocks, one kv head each
   float* ring = reinterpret_cast<float*>(flat_smem) + (size_t)warp * STAGES * (kTileBytes / 4);
 
   if (lane == 0) {
@@ -255,8 +283,11 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
   // never on the path between two tiles.  The first tiles' physical blocks come with the warp's start record.
   int s0 = 0, s1 = 0, is = 0, ji = 0, ilb = 0, pb_next = -1, first_lb0 = 0;
   int4 ia = make_int4(0, 0, 0, 0), hpb = make_int4(-1, -1, -1, 0);
-  bool iq = true;
+  bool iq = true, bad = false;
   uint32_t pre_issued = 0;   // items whose copy went out before the dependency wait
+  auto seg_ok = [&](const int4& sg) {
+    return (unsigned)sg.x < (unsigned)p.B && (unsigned)sg.y < (unsigned)KVH && sg.z >= 0 && sg.z < sg.w && sg.w <= p.max_blocks;
+  };
   auto copy_tile = [&](int item, int kvh, int pb) {   // lane 0
     const uint32_t bar = attn_smem_u32(&bars[warp][item % STAGES]);
     const uint32_t dst = attn_smem_u32(ring + (size_t)(item % STAGES) * (kTileBytes / 4));
@@ -271,6 +302,11 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
     const int4 h0 = p.hdr[kHdrWords * wslot];
     s0 = h0.x;
     s1 = h0.y;
+    if (s0 < 0 || s1 < s0 || s1 * KVH > p.max_slots) {
+      if (lane == 0) flat_report(p.err_flag, 11, wslot, s0, s1, make_int4(0, 0, 0, 0), -1, -1);
+      s0 = s1 = 0;
+      bad = true;
+    }
     if (s0 < s1) {
       ia = p.hdr[kHdrWords * wslot + 1];
       hpb = p.hdr[kHdrWords * wslot + 3];
@@ -283,8 +319,8 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
     // the first tiles of the ring go out before the dependency wait (items 1.. ; item 0 is the query rows).
     const int safe = read_header();
     have_header = true;
-    if (lane == 0 && s0 < s1)
-      for (int k = 0; k + 1 < STAGES && ia.z + k < min(ia.w, safe); ++k) {
+    if (lane == 0 && s0 < s1 && seg_ok(ia))
+      for (int k = 0; k + 1 < STAGES && ia.z + k < min(ia.w, safe) && (unsigned)hdr_pb(k) < (unsigned)p.L.num_blocks; ++k) {
         copy_tile(k + 1, ia.y, hdr_pb(k));
         pre_issued |= 1u << (k + 1);
       }
@@ -292,20 +328,28 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
   }
   pi_grid_dependency_wait();   // the work list (unless settled), the query rows and this step's K/V rows come from kernels ahead
   if (!have_header) read_header();
+  is = s0;   // a slot without segments (s0 == s1) issues nothing
   if (s0 < s1) {
-    is = s0;
     ilb = ia.z;
     first_lb0 = ia.z;
     pb_next = hpb.x;
   }
   bool cache_ready = false;   // s_segs holds this warp's first segments
   auto seg_word = [&](int s, int half) -> int4 {
-    return (cache_ready && s - s0 < kSegCap) ? s_segs[warp][2 * (s - s0) + half] : __ldg(&p.segs[2 * s + half]);
+    int4 v = (cache_ready && s - s0 < kSegCap) ? s_segs[warp][2 * (s - s0) + half] : __ldg(&p.segs[2 * s + half]);
+    if (half == 0) v.y = my_kvh;   // the list is shared by the group's warps
+    return v;
   };
   auto issue_one = [&]() {
     const uint32_t bar = attn_smem_u32(&bars[warp][ji % STAGES]);
     const uint32_t dst = attn_smem_u32(ring + (size_t)(ji % STAGES) * (kTileBytes / 4));
     if (iq) {
+      if (!seg_ok(ia)) {
+        if (lane == 0) flat_report(p.err_flag, 12, wslot, s0, s1, ia, -1, ji);
+        bad = true;
+        is = s1;   // nothing further goes out
+        return;
+      }
       if (lane == 0) {
         const float* src = p.q + (size_t)ia.x * p.q_stride + (size_t)ia.y * G * HD;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kQBytes) : "memory");
@@ -315,7 +359,14 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
       }
       iq = false;
     } else {
-      if (lane == 0 && !(ji < STAGES && ((pre_issued >> ji) & 1u))) copy_tile(ji, ia.y, pb_next);
+      const int pbv = __shfl_sync(0xffffffffu, pb_next, 0);
+      if ((unsigned)pbv >= (unsigned)p.L.num_blocks) {
+        if (lane == 0) flat_report(p.err_flag, 13, wslot, s0, s1, ia, pbv, ji);
+        bad = true;
+        is = s1;
+        return;
+      }
+      if (lane == 0 && !(ji < STAGES && ((pre_issued >> ji) & 1u))) copy_tile(ji, ia.y, pbv);
       if (++ilb >= ia.w) {
         if (++is < s1) {
           ia = seg_word(is, 0);
@@ -324,7 +375,9 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
         }
       }
       if (lane == 0 && is < s1)
-        pb_next = (is == s0 && ilb - first_lb0 < 3) ? hdr_pb(ilb - first_lb0) : p.tables[(size_t)ia.x * p.max_blocks + ilb];
+        pb_next = (is == s0 && ilb - first_lb0 < 3) ? hdr_pb(ilb - first_lb0)
+                  : (seg_ok(ia) && ilb < ia.w)      ? p.tables[(size_t)ia.x * p.max_blocks + ilb]
+                                                    : -1;   // reported when the copy is due
     }
     ++ji;
   };
@@ -361,10 +414,15 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
   for (int cs = s0; cs < s1; ++cs) {
     const int4 sa = seg_word(cs, 0), sb = seg_word(cs, 1);
     const int b = sa.x, kvh = sa.y, lb0 = sa.z, lb1 = sa.w, pos = sb.x, st = sb.y;
+    if (!seg_ok(sa)) {
+      if (lane == 0) flat_report(p.err_flag, 12, wslot, s0, s1, sa, -1, -2);
+      failed = bad = true;
+      break;
+    }
     const int2 cm = __ldg(&p.comb[b * KVH + kvh]);   // needed at the end of the segment only
 
     // ---- the query rows: 8 dims per lane (16-byte chunks li and li + LPT of the head) for every head of the group
-    if (!wait_item(jc)) { failed = true; break; }
+    if (jc >= ji || !wait_item(jc)) { failed = true; break; }
     float2 qv[G][4];
     {
       const float* qs = ring + (size_t)(jc % STAGES) * (kTileBytes / 4);
@@ -390,19 +448,12 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
 
 #pragma unroll 1
     for (int lb = lb0; lb < lb1; ++lb) {
-      if (!wait_item(jc)) { failed = true; break; }
+      if (jc >= ji || !wait_item(jc)) { failed = true; break; }
       const int t_lo = max(st - lb * BS, 0), t_hi = min(pos - lb * BS, BS - 1);
       const bool whole = (t_lo == 0) && (t_hi == BS - 1);
       const float* Kt = ring + (size_t)(jc % STAGES) * (kTileBytes / 4);
       const float* Vt = Kt + BS * HD;
 
-#ifdef PI_FLAT_PROBE_NOMATH   // timing probe only: the ring without the arithmetic (results are meaningless)
-      acc[0][0].x += Kt[lane] + Vt[lane] + (whole ? 0.f : 1.f);
-      __syncwarp();
-      if (is < s1) issue_one();
-      ++jc;
-      continue;
-#endif
       // ---- A: scores -----------------------------------------------------------------------------------------
       float sc[STEPS];
 #pragma unroll
@@ -504,9 +555,14 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
     float l_all = l_own * f_own;
 #pragma unroll
     for (int o = LPT; o < 32; o <<= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, o);
+    if (cm.y < 1 || cm.x < 0 || (cm.x + cm.y) * KVH > p.max_slots || cs < cm.x || cs >= cm.x + cm.y) {
+      if (lane == 0) flat_report(p.err_flag, 12, wslot, s0, s1, make_int4(b, kvh, cm.x, cm.y), -1, -3);
+      failed = bad = true;
+      break;
+    }
     const bool direct = cm.y == 1;   // this segment is the whole window: normalise and write the output rows
     const float inv_own = 1.0f / fmaxf(l_all, 1e-12f);
-    const int slot = cs;             // a segment's partial slot is its index
+    const int slot = cs * KVH + kvh; // a partial's slot: (group segment, kv head)
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const int src_lane = lane_base + attn_owner_lane<G, LPT>(g);
@@ -556,7 +612,7 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
         const int g = min(lane / LH, G - 1), dq = lane % LH;
         const bool active = lane / LH < G;
         float M = -INFINITY;
-        for (int i = 0; i < cnt; ++i) M = fmaxf(M, __ldcg(p.part_ml + ((size_t)(first + i) * G + g) * 2));
+        for (int i = 0; i < cnt; ++i) M = fmaxf(M, __ldcg(p.part_ml + ((size_t)((first + i) * KVH + kvh) * G + g) * 2));
         float ls = 0.f;
         float4 av[IPL];
 #pragma unroll
@@ -568,10 +624,11 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int i = min(i0 + u, cnt - 1);
-            ml[u] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((size_t)(first + i) * G + g) * 2));
+            const size_t sl = (size_t)(first + i) * KVH + kvh;
+            ml[u] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (sl * G + g) * 2));
 #pragma unroll
             for (int it = 0; it < IPL; ++it)
-              pa[u][it] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + ((size_t)(first + i) * G + g) * HD + (dq + it * LH) * 4));
+              pa[u][it] = __ldcg(reinterpret_cast<const float4*>(p.part_acc + (sl * G + g) * HD + (dq + it * LH) * 4));
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
@@ -595,8 +652,8 @@ __global__ void __launch_bounds__(kFlatWarps * 32) attn_decode_flat_kernel(const
   }
 
   if (failed) {
-    if (lane == 0 && p.err_flag) atomicExch(p.err_flag, 7);
-    for (int jj = jc + 1; jj < ji; ++jj) wait_item(jj);   // bounded drain of the copies still in flight
+    if (lane == 0 && p.err_flag && !bad) atomicExch(p.err_flag, 7);
+    for (int jj = jc; jj < ji; ++jj) wait_item(jj);   // bounded drain of the copies still in flight
   }
 }
 
@@ -741,6 +798,7 @@ pi_status pi_launch_attention_flat(pi_ctx* ctx, const pi_kv_pool* pool, int laye
   p.max_blocks = batch.max_blocks;
   p.hdr = static_cast<const int4*>(batch.flat_hdr);
   p.plan_settled = batch.flat_settled ? 1 : 0;
+  p.max_slots = (int)batch.flat_slots;
   p.segs = static_cast<const int4*>(batch.flat_segs);
   p.comb = static_cast<const int2*>(batch.flat_comb);
   p.counters = batch.flat_counters;

@@ -40,11 +40,22 @@ void pi_set_global_error(const char* msg);
     if (!(cond)) return pi_fail((ctx), PI_ERR_INVALID_ARG, __VA_ARGS__); \
   } while (0)
 
+// First line of an API entry point: a null context is an argument error; a host thread whose current device is not
+// the context's is switched to it (every launch, copy and allocation below goes to the current device).
+#define PI_ENTER(ctx)                              \
+  do {                                             \
+    if (!(ctx)) return PI_ERR_INVALID_ARG;         \
+    pi_status _se = pi_enter(ctx);                 \
+    if (_se != PI_OK) return _se;                  \
+  } while (0)
+
 #define PI_TRY(expr)               \
   do {                             \
     pi_status _s = (expr);         \
     if (_s != PI_OK) return _s;    \
   } while (0)
+
+constexpr int PI_DEV_ERR_WORDS = 16;
 
 // ---- context ------------------------------------------------------------------
 // A growable device buffer owned by the context (scratch that outlives a call).
@@ -61,7 +72,7 @@ struct pi_ctx {
   size_t smem_optin = 0;
   std::string err;
   uint64_t launches = 0;
-  int* dev_err = nullptr;   // device word set by a kernel whose bounded wait ran out
+  int* dev_err = nullptr;   // device words: [0] set by a kernel that gave up (bounded wait ran out, inconsistent input), [1..] its record
 
   // tensor parallelism
   int rank = 0, tp = 1;
@@ -116,6 +127,7 @@ struct pi_prof_scope {
   ~pi_prof_scope();
 };
 
+pi_status pi_enter(pi_ctx* ctx);
 pi_status pi_reserve(pi_ctx* ctx, pi_buffer* buf, size_t bytes);
 pi_status pi_reserve_pinned(pi_ctx* ctx, size_t bytes);
 

@@ -759,7 +759,7 @@ static pi_status noalloc_scratch_address(pi_ctx* ctx, void** out) {
 }
 
 extern "C" pi_status pi_linear_apply_noalloc(pi_ctx* ctx, const pi_linear* lin, const float* x_dev, float* out_dev, int M) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, lin && x_dev && out_dev, "null pointer");
   PI_REQUIRE(ctx, M >= 1 && M <= kNoAllocMaxM, "batch %d is outside the built-in scratch (1..%d activation rows)", M, kNoAllocMaxM);
   PI_REQUIRE(ctx, lin->cols <= (size_t)kNoAllocMaxK, "%zu columns exceed the built-in scratch (at most %d)", lin->cols, kNoAllocMaxK);

@@ -149,7 +149,23 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   __shared__ int sk[32], si[32];
   const float* row = logits + (size_t)blockIdx.x * stride;
   int bk = INT_MIN, bi = -1;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) argmax_merge(bk, bi, total_order_key(row[i]), i);
+  if ((((uintptr_t)row) & 15) == 0) {
+    // four independent candidates per thread over 16-byte loads, merged in index order afterwards
+    int k4[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN}, i4[4] = {-1, -1, -1, -1};
+    const int n4 = n >> 2;
+    for (int v = threadIdx.x; v < n4; v += blockDim.x) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(row) + v);
+      argmax_merge(k4[0], i4[0], total_order_key(f.x), 4 * v);
+      argmax_merge(k4[1], i4[1], total_order_key(f.y), 4 * v + 1);
+      argmax_merge(k4[2], i4[2], total_order_key(f.z), 4 * v + 2);
+      argmax_merge(k4[3], i4[3], total_order_key(f.w), 4 * v + 3);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) argmax_merge(bk, bi, k4[j], i4[j]);
+    for (int i = 4 * n4 + threadIdx.x; i < n; i += blockDim.x) argmax_merge(bk, bi, total_order_key(row[i]), i);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) argmax_merge(bk, bi, total_order_key(row[i]), i);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const int k = __shfl_xor_sync(0xffffffffu, bk, o), i = __shfl_xor_sync(0xffffffffu, bi, o);

@@ -555,7 +555,7 @@ pi_status stage_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t
 extern "C" {
 
 pi_status pi_model_create(pi_ctx* ctx, const pi_model_config* cfg, const pi_model_weights* w, pi_model** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, cfg && w && out, "null pointer");
   *out = nullptr;
   PI_TRY(validate_config(ctx, cfg));
@@ -586,7 +586,7 @@ pi_status pi_model_create(pi_ctx* ctx, const pi_model_config* cfg, const pi_mode
 
 pi_status pi_model_create_synthetic(pi_ctx* ctx, const pi_model_config* cfg, uint64_t seed, float std, int quant,
                                     int lm_head_kind, pi_model** out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, cfg && out, "null pointer");
   *out = nullptr;
   PI_TRY(validate_config(ctx, cfg));
@@ -650,7 +650,7 @@ pi_status pi_model_decode_batch_rows(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool,
                                      const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,
                                      const int32_t* table_lens_host, int B, const int32_t* logit_rows_host, int n_logit_rows,
                                      float* logits_host, uint32_t* argmax_host) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, m && argmax_host, "null pointer");
   PI_REQUIRE(ctx, n_logit_rows >= 0 && n_logit_rows <= B && (n_logit_rows == 0 || (logit_rows_host && logits_host)),
              "%d rows of logits were asked for out of %d", n_logit_rows, B);
@@ -672,7 +672,7 @@ pi_status pi_model_decode_batch(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
                                 const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,
                                 const int32_t* table_lens_host, int B, float* logits_host_or_null,
                                 uint32_t* argmax_host_or_null) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, m && tokens_host && positions_host && table_lens_host, "null pointer");
   PI_REQUIRE(ctx, block_tables_host || max_blocks == 0, "null block tables");
   PI_REQUIRE(ctx, B > 0, "decode_batch_into needs at least one sequence");
@@ -747,7 +747,7 @@ static pi_status decode_one_step(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, con
 pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host,
                                 const int32_t* positions_host, const int32_t* block_tables_host, int max_blocks,
                                 const int32_t* table_lens_host, int B, int n_steps, uint32_t* out_tokens_host) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, m && tokens_host && positions_host && table_lens_host && out_tokens_host, "null pointer");
   PI_REQUIRE(ctx, block_tables_host || max_blocks == 0, "null block tables");
   PI_REQUIRE(ctx, B > 0, "decode needs at least one sequence");
@@ -815,7 +815,7 @@ pi_status pi_model_decode_multi(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, cons
 pi_status pi_model_prefill(pi_ctx* ctx, pi_model* m, pi_kv_pool* pool, const uint32_t* tokens_host, int n, int start_pos,
                            const int32_t* block_table_host, int table_len, int chunk, float* last_logits_host_or_null,
                            uint32_t* argmax_host_or_null) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, m && tokens_host, "null pointer");
   PI_REQUIRE(ctx, n > 0, "prefill needs at least one token");
   PI_REQUIRE(ctx, start_pos >= 0 && table_len >= 0, "negative start position or table length");

@@ -258,7 +258,7 @@ size_t peer_flags_offset(size_t slot_floats, int tp) { return (size_t)kPeerSlots
 }  // namespace
 
 extern "C" pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* handle_out) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, handle_out && max_floats > 0, "null pointer or empty buffer");
   PI_REQUIRE(ctx, ctx->tp > 1 && ctx->tp <= kPeerMaxTp, "the peer path needs a tensor-parallel context");
   PI_REQUIRE(ctx, !ctx->peer.base, "the peer buffers of this context exist already");
@@ -276,7 +276,7 @@ extern "C" pi_status pi_tp_peer_export(pi_ctx* ctx, size_t max_floats, void* han
 }
 
 extern "C" pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, handles && ctx->peer.base, "call pi_tp_peer_export first");
   const unsigned char* all = static_cast<const unsigned char*>(handles);
   for (int r = 0; r < ctx->tp; ++r) {
@@ -298,7 +298,7 @@ extern "C" pi_status pi_tp_peer_import(pi_ctx* ctx, const void* handles) {
 extern "C" void* pi_tp_peer_base(const pi_ctx* ctx) { return ctx ? ctx->peer.base : nullptr; }
 
 extern "C" pi_status pi_tp_peer_import_pointers(pi_ctx* ctx, void* const* bases) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, bases && ctx->peer.base, "call pi_tp_peer_export first");
   PI_REQUIRE(ctx, bases[ctx->rank] == ctx->peer.base, "entry %d of the pointer table must be this context's own buffer", ctx->rank);
   for (int r = 0; r < ctx->tp; ++r) {
@@ -312,7 +312,7 @@ extern "C" pi_status pi_tp_peer_import_pointers(pi_ctx* ctx, void* const* bases)
 }
 
 extern "C" pi_status pi_tp_exchange_add(pi_ctx* ctx, const float* partial_dev, float* x_dev, int rows, int cols) {
-  if (!ctx) return PI_ERR_INVALID_ARG;
+  PI_ENTER(ctx);
   PI_REQUIRE(ctx, partial_dev && x_dev && rows > 0 && cols > 0, "null pointer or empty matrix");
   const size_t n = (size_t)rows * cols;
   if (ctx->tp == 1) return pi_launch_add(ctx, x_dev, partial_dev, n);
