@@ -518,7 +518,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         kv_bytes_layer = eb.unique_mapped_tokens() * KH * 2 * hd * 4
         algo = {"attention": kv_bytes_layer + 2 * B * H * hd * 4,
                 "gemv": weight_bytes / max(prof["gemv"][1] / P, 1), "gemm_tc": weight_bytes / max(prof["gemm_tc"][1] / P, 1)}
-        names = {"attention": "attn_decode_v3_kernel<64,8,3> (+ split merge): one layer, 64 sequences",
+        names = {"attention": "attn_decode_flat_kernel<64,8,3> (one layer, 64 sequences; the step's one attn_plan_kernel launch is spread over the layers)"
+                              if not args.attn_grid else "attn_decode_v3_kernel<64,8,3> + attn_combine_kernel: one layer, 64 sequences",
                  "gemv": "gemv_kernel<int8>: CUDA-core dequant projections of the step",
                  "gemm_tc": "gemm_ta_kernel<64,4>: tcgen05 dequant projections of the step (average over its launches)"}
         rl = {}
@@ -526,6 +527,8 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
             ms, n = prof[cls]
             if n == 0:
                 continue
+            if cls == "attention":
+                n = NL * P          # per layer: the work-list kernel (once per step) and the merge kernel are part of the layer's attention
             us_serial = ms * 1e3 / n
             # inside the timed region launches overlap their predecessor's tail (programmatic dependent launch); the
             # events that bracket every launch here serialise them.  Duration inside the step = this class's share
