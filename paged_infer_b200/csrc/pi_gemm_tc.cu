@@ -52,7 +52,9 @@ namespace cg = cooperative_groups;
 namespace {
 using namespace pi_tc;
 
-template <int BN, int STAGES>
+// PUSH (launches whose K is split over a cluster): the partial tiles meet by remote stores into a receive area of the
+// CTA that owns the column, behind the pipeline stages, instead of by remote loads from every CTA's parked tile.
+template <int BN, int STAGES, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) {
   constexpr int kBAtomBytes = kPlanes * BN * 128;           // one 64-element K atom: BN rows of plane 0, 1, 2
@@ -111,6 +113,9 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // A CTA's shared memory may only be written by its cluster peers once it runs: everybody says so now and checks,
+  // for free, right before the first remote store of the epilogue.
+  if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   // Every thread releases the dependent grid (the release only happens once all threads of all CTAs have done so):
   // the next kernels then sit resident, with their own prologue done, by the time this one ends.  Only now that this
   // CTA holds its tensor memory: a dependent CTA that took the SM's columns first would keep them until this grid
@@ -237,15 +242,17 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
   const uint32_t my_d = tmem + ((uint32_t)(quad * 32) << 16);
 
   {
-    // Every CTA parks its raw partial tile in its own shared memory (the pipeline stages are free by now).  When K
-    // was split over the CTAs of a thread-block cluster (cluster rank = K slice) the cluster synchronises and each
-    // CTA adds up and emits 1/ksplit of the tile's columns, reading its peers' tiles through distributed shared
-    // memory in rank order - so the sum does not depend on timing.  A single CTA goes the same way with itself as
-    // the only rank: the detour through shared memory turns the row-per-lane accumulator layout into four
-    // adjacent output columns per thread, so every store below is 8 or 16 bytes wide.
-    const bool clustered = p.ksplit > 1;
+    // The raw partial tile goes from tensor memory through shared memory: the detour turns the row-per-lane accumulator
+    // layout into four adjacent output columns per thread, so every store below is 8 or 16 bytes wide.  When K was
+    // split over the CTAs of a thread-block cluster (cluster rank = K slice), column c of the tile is finished by
+    // rank c % ksplit: every rank stores its values of that column straight into the owner's receive area
+    // (distributed shared memory), one cluster barrier later the owner adds the slices in rank order.
     cg::cluster_group cluster = cg::this_cluster();
-    float* my_part = reinterpret_cast<float*>(smem);  // [BN][128]
+    const int rank = PUSH ? (int)cluster.block_rank() : 0, nranks = PUSH ? p.ksplit : 1;
+    const int cpo = (BN + nranks - 1) / nranks;                // columns an owner receives from each rank
+    float* my_part = reinterpret_cast<float*>(smem);          // !PUSH: [BN][128] over the (free) pipeline stages
+    float* recv = reinterpret_cast<float*>(smem + STAGES * kBStageBytes);   // PUSH: [nranks][cpo][128]
+    if (PUSH) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // every peer runs (arrived long ago)
     if (epi_warp) {
 #pragma unroll 1
       for (int c0 = half * kColsPerHalf; c0 < (half + 1) * kColsPerHalf && c0 < BN; c0 += 16) {
@@ -256,34 +263,55 @@ gemm_ta_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_act) 
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
+        if (PUSH) {
+          // column c belongs to rank c % nranks, as its column c / nranks; this rank's values go to slice `rank` there
+          int owner = c0 % nranks, idx = c0 / nranks;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) my_part[(c0 + j) * kBM + quad * 32 + lane] = v[j];
+          for (int j = 0; j < 16; ++j) {
+            float* dst = cluster.map_shared_rank(recv, owner) + ((size_t)(rank * cpo + idx) * kBM + quad * 32 + lane);
+            *dst = v[j];
+            if (++owner == nranks) {
+              owner = 0;
+              ++idx;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) my_part[(c0 + j) * kBM + quad * 32 + lane] = v[j];
+        }
       }
     }
-    // this thread's four rows: scales and emit norm weights are fetched while the cluster barrier is pending
+    // this thread's four rows: scales and emit norm weights are fetched while the barrier is pending
     const int r4 = (tid & 31) * 4, csub = tid >> 5;  // 16 columns in flight per pass
     EpiRows rows;
     epi_rows_load(p, row0, tid, rows);
-    if (clustered) cluster.sync(); else __syncthreads();
-    const int rank = clustered ? (int)cluster.block_rank() : 0, nranks = p.ksplit;
+    if (PUSH) {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // all partials of this CTA's columns are here
+    } else {
+      __syncthreads();
+    }
     if (tid < kProducerWarps * 32) {
       for (int c = rank + csub * nranks; c < BN; c += kProducerWarps * nranks) {
-        // all peers' slices are requested before the first add (one remote latency instead of nranks), the adds
-        // stay in rank order
-        float4 part[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          part[r] = r < nranks ? *reinterpret_cast<const float4*>((clustered ? cluster.map_shared_rank(my_part, r) : my_part) + c * kBM + r4)
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        // the adds stay in rank order, so the sum does not depend on timing
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (PUSH) {
+          const int idx = c / nranks;
+          float4 part[8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+          for (int r = 0; r < 8; ++r)
+            part[r] = r < nranks ? *reinterpret_cast<const float4*>(recv + (size_t)(r * cpo + idx) * kBM + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+          }
+        } else {
+          acc = *reinterpret_cast<const float4*>(my_part + c * kBM + r4);
         }
         epi_row(p, rows, blockIdx.x, m0 + c, s_rowf[c], acc, tid & 31);
       }
     }
-    if (clustered) cluster.sync();  // nobody leaves while a peer may still be reading its tile
+    // nobody reads or writes a peer's shared memory after the barrier above: a CTA may leave as soon as it is done
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -408,10 +436,17 @@ EncodeTiledFn encode_tiled() {
 }
 
 
-template <int BN, int STAGES>
+// Dynamic shared memory of an instantiation: the pipeline stages, the receive area of the cluster reduction (PUSH: up
+// to BN + 7 columns of 128 rows, rounded up), alignment slack; never less than what keeps two CTAs off one SM.
+template <int BN, int STAGES, bool PUSH>
+constexpr size_t ta_smem_bytes() {
+  return std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + (PUSH ? (size_t)(BN + 8) * kBM * sizeof(float) : 0) + 1024, kMinSmem);
+}
+
+template <int BN, int STAGES, bool PUSH>
 cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, dim3 grid) {
-  constexpr size_t smem = std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + 1024, kMinSmem);
-  auto k = gemm_ta_kernel<BN, STAGES>;
+  constexpr size_t smem = ta_smem_bytes<BN, STAGES, PUSH>();
+  auto k = gemm_ta_kernel<BN, STAGES, PUSH>;
   static pi_smem_grant granted;  // per instantiation
   if (smem > granted.of(ctx)) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -444,13 +479,13 @@ cudaError_t launch_ta(pi_ctx* ctx, const GemmParams& p, const CUtensorMap& act, 
 
 // How many clusters of `ksplit` CTAs of this kernel the device can hold at once (clusters are placed inside one GPC,
 // so this is less than SMs / ksplit); asked once per cluster size.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PUSH>
 int max_clusters(pi_ctx* ctx, int ksplit) {
   static int cached[9] = {};
   if (ksplit < 2 || ksplit > 8) return ctx->sm_count;
   if (!cached[ksplit]) {
-    constexpr size_t smem = std::max((size_t)STAGES * (2 * kPlanes * BN * 128) + 1024, kMinSmem);
-    auto k = gemm_ta_kernel<BN, STAGES>;
+    constexpr size_t smem = ta_smem_bytes<BN, STAGES, PUSH>();
+    auto k = gemm_ta_kernel<BN, STAGES, PUSH>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, ksplit, 1);
@@ -475,9 +510,9 @@ int max_clusters(pi_ctx* ctx, int ksplit) {
 
 int max_clusters_bn(pi_ctx* ctx, int BN, int ksplit) {
   switch (BN) {
-    case 16: return max_clusters<16, 6>(ctx, ksplit);
-    case 32: return max_clusters<32, 6>(ctx, ksplit);
-    default: return max_clusters<64, 4>(ctx, ksplit);
+    case 16: return max_clusters<16, 6, true>(ctx, ksplit);
+    case 32: return max_clusters<32, 6, true>(ctx, ksplit);
+    default: return max_clusters<64, 3, true>(ctx, ksplit);
   }
 }
 
@@ -602,10 +637,20 @@ pi_status run_gemm(pi_ctx* ctx, const pi_linear* lin, const pi_linear_args& a, c
   p.ksplit = ksplit;
   const dim3 grid(rtiles, ksplit, mtiles);
   cudaError_t err;
-  switch (BN) {
-    case 16: err = launch_ta<16, 6>(ctx, p, map, grid); break;
-    case 32: err = launch_ta<32, 6>(ctx, p, map, grid); break;
-    default: err = launch_ta<64, 4>(ctx, p, map, grid); break;
+  // K split over a cluster: the instantiation with the receive area of the reduction (at 64 activation rows one stage
+  // less, a CTA of such a launch has few K blocks anyway)
+  if (ksplit > 1) {
+    switch (BN) {
+      case 16: err = launch_ta<16, 6, true>(ctx, p, map, grid); break;
+      case 32: err = launch_ta<32, 6, true>(ctx, p, map, grid); break;
+      default: err = launch_ta<64, 3, true>(ctx, p, map, grid); break;
+    }
+  } else {
+    switch (BN) {
+      case 16: err = launch_ta<16, 6, false>(ctx, p, map, grid); break;
+      case 32: err = launch_ta<32, 6, false>(ctx, p, map, grid); break;
+      default: err = launch_ta<64, 4, false>(ctx, p, map, grid); break;
+    }
   }
   if (err != cudaSuccess) return pi_fail(ctx, PI_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(err));
   ctx->launches++;
