@@ -812,8 +812,8 @@ def run_kernel_case(args):
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = api.Context(0, stream=tstream.cuda_stream)
-    if args.attn_grid:
-        ctx.set_option(api._lib.PI_OPT_ATTN_FLAT, 0)
+    # a single attention call takes the flat tile list only on request (it pays for its own work-list kernel)
+    ctx.set_option(api._lib.PI_OPT_ATTN_FLAT, 0 if args.attn_grid else 2)
     rng = np.random.default_rng(11)
     reps = max(args.steps, 1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

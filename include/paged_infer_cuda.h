@@ -121,7 +121,8 @@ pi_status pi_ctx_profile_end(pi_ctx* ctx, double* ms_out /*[PI_PROF_CLASSES]*/, 
 enum { PI_OPT_TENSOR_GEMM = 1, PI_OPT_CUDA_GRAPH = 2, PI_OPT_PDL = 3, PI_OPT_GEMV_MAX_M = 4, PI_OPT_ATTN_TMA = 5, PI_OPT_FUSE_PLANES = 6, PI_OPT_ATTN_SHARED = 7,
        PI_OPT_PEER_SPIN_LIMIT = 8 /* polls, 64 ns apart, that a rank waits for a peer's partial sums; 0 = default */,
        PI_OPT_TP_PUSH = 9 /* peer path: row-split projections store their partial sums into every rank's buffer themselves */,
-       PI_OPT_ATTN_FLAT = 10 /* batched decode attention over one flat tile list cut into equal ranges per resident warp */ };
+       PI_OPT_ATTN_FLAT = 10 /* batched decode attention over one flat tile list cut into equal ranges per resident warp:
+                                0 never, 1 (default) inside a model forward, 2 also for a single pi_paged_attention call */ };
 pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value);
 
 /* ---- quantiser --------------------------------------------------------------- */

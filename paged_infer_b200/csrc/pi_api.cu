@@ -231,7 +231,10 @@ pi_status pi_ctx_set_option(pi_ctx* ctx, int option, int value) {
     case PI_OPT_ATTN_SHARED: ctx->opt_attn_shared = value; return PI_OK;
     case PI_OPT_FUSE_PLANES: ctx->opt_fuse_planes = value != 0; return PI_OK;
     case PI_OPT_TP_PUSH: ctx->opt_tp_push = value != 0; return PI_OK;
-    case PI_OPT_ATTN_FLAT: ctx->opt_attn_flat = value != 0; return PI_OK;
+    case PI_OPT_ATTN_FLAT:
+      if (value < 0 || value > 2) return pi_fail(ctx, PI_ERR_INVALID_ARG, "PI_OPT_ATTN_FLAT is 0, 1 or 2");
+      ctx->opt_attn_flat = value;
+      return PI_OK;
     case PI_OPT_PEER_SPIN_LIMIT:
       PI_REQUIRE(ctx, value >= 0, "the spin limit cannot be negative");
       ctx->peer_spin_limit = (uint32_t)value;
@@ -599,7 +602,7 @@ pi_status pi_paged_attention(pi_ctx* ctx, const pi_kv_pool* pool, int layer, int
   pi_attn_batch batch;
   PI_TRY(pi_upload_attn_batch(ctx, block_tables_host, max_blocks, table_lens_host, pos_host, start_host, B,
                               pool->L.block_size, pool->L.num_blocks, &batch));
-  PI_TRY(pi_attention_prepare(ctx, pool, num_heads, batch));
+  if (ctx->opt_attn_flat >= 2) PI_TRY(pi_attention_prepare(ctx, pool, num_heads, batch));
   return pi_launch_attention(ctx, pool, layer, num_heads, q_dev, q_stride, out_dev, out_stride, batch);
 }
 

@@ -98,7 +98,10 @@ struct pi_ctx {
   int opt_gemv_max_m = 4;
   int opt_attn_shared = 1;   // entries that share one block table: 0 decode kernel, 1 shared-table kernel when it fills the GPU, 2 always, 3 always and on the mma.sync kernel
   int opt_attn_tma = 1;   // 0 direct loads, 1 tile-at-a-time kernel (block size 16) over a TMA ring, 2 per-token kernel over a TMA ring
-  bool opt_attn_flat = true;   // batched decode with many tiles: one equal range of the batch's tile list per resident warp
+  // batched decode with many tiles over one flat tile list (an equal range per resident warp): 0 never, 1 inside a
+  // model forward, where one work list serves all layers of the step, 2 also for a single pi_paged_attention call
+  // (which then pays for its own work-list kernel: slower than the per-entry grid, there for tests)
+  int opt_attn_flat = 1;
   bool opt_tp_push = true;  // tensor parallel, peer path: row-split projections push their partial sums into every rank's buffer
   int opt_fuse_planes = 1;  // model forward: projections hand their result to the next one as bf16 planes (no split kernel)
 

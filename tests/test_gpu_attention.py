@@ -142,7 +142,7 @@ def test_flat_work_list_ragged_batch(ctx, oracle, hd, H, KH, batch, blocks):
     tables[6] = tables[6][:pos[6] // bs // 2]   # the table ends long before the position
     st[7] = (pos[7] // bs) * bs              # window starts on the position's own block
     want = cpu_run(oracle, case, q, tables, pos, st)
-    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 1)
+    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 2)     # also for a single attention call (1: inside a model forward only)
     got = gpu_run(ctx, case, q, tables, pos, st)
     again = gpu_run(ctx, case, q, tables, pos, st)
     ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 0)
