@@ -325,3 +325,41 @@ def test_multi_step_decode_equals_step_by_step(ctx, oracle):
             assert multi[s].tolist() == cur.tolist(), (B, s)
             pos = [p + 1 for p in pos]
         assert np.abs(kv_a.download() - kv_b.download()).max() < 1e-5
+
+
+def test_multi_step_decode_over_the_flat_work_list(ctx, oracle):
+    """A batch with enough K|V tiles for the flat attention work list (64 sequences of 600-700 tokens): the work list is
+    rebuilt on the device from the positions every step, so n steps inside one call (CUDA graph, positions advanced on
+    the device, blocks crossed on the way) must give the ids and the KV of n single-step calls; the
+    per-entry grid (option off) must agree on the logits to rounding."""
+    from paged_infer_b200 import _lib, api
+    cfg, om, gm = small_llama(ctx, oracle, 8)
+    rng = np.random.default_rng(8)
+    B, n, nblk = 64, 20, 46
+    pos0 = [int(x) for x in rng.integers(600, 700, B)]
+    tables = [[int(t) for t in rng.permutation(nblk) + b * nblk] for b in range(B)]
+    caches = []
+    for _ in range(3):
+        kv = api.KvCache(ctx, gm.kv_layout(nblk * B, BLOCK))
+        kv.fill_normal(3, 1.0)
+        caches.append(kv)
+    tok = rng.integers(0, cfg.vocab_size, B).astype(np.uint32)
+    launches0 = ctx.kernel_launches()
+    multi = gm.decode_multi(tok, pos0, tables, caches[0], n)
+    per_step = (ctx.kernel_launches() - launches0) / n
+    cur, pos = tok, list(pos0)
+    for s in range(n):
+        cur = gm.decode_batch_into(cur, pos, tables, caches[1], want_logits=False, want_argmax=True)
+        assert multi[s].tolist() == cur.tolist(), s
+        pos = [p + 1 for p in pos]
+    assert np.abs(caches[0].download() - caches[1].download()).max() < 1e-6
+    # one launch per layer for the attention (no merge launch) + the work list: 5 per layer + embed, planes, LM head, argmax, advance
+    assert per_step <= 5 * cfg.num_hidden_layers + 7, per_step
+    flat_logits, _ = gm.decode_batch_into(tok, pos0, tables, caches[2], want_argmax=True)
+    ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 0)
+    try:
+        grid_logits, _ = gm.decode_batch_into(tok, pos0, tables, caches[2], want_argmax=True)
+    finally:
+        ctx.set_option(_lib.PI_OPT_ATTN_FLAT, 1)
+    assert np.abs(flat_logits - grid_logits).max() < 1e-4
+    assert not np.array_equal(flat_logits, grid_logits), "the flat work list was not used"
