@@ -567,6 +567,16 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         bytes1 = weight_bytes + (128 + 64 + 1) * KH * 2 * hd * 4 * NL
         batch1 = {"tok/s": round(1e3 / ms1, 1), "ms_per_step": round(ms1, 4), "roofline_tok/s": round(hbm_peak * 1e9 / bytes1, 1),
                   "frac_of_hbm_roofline": round((bytes1 / (ms1 / 1e3)) / (hbm_peak * 1e9), 3), "bytes_per_step": bytes1}
+        # the same steps with CUDA events around every launch: what a projection costs INSIDE the step (the back-to-back
+        # figures of `gemv_m1` have no dependent kernel ahead of them)
+        ctx.profile_begin()
+        model.decode_multi([1], [192], t1, kvb1, 16)
+        prof1 = ctx.profile_end()
+        tot1 = sum(ms for ms, _ in prof1.values()) or 1e-9
+        batch1["in_step"] = {c: {"launches_per_step": n / 16, "share": round(ms / tot1, 3),
+                                 "us_per_launch": round((ms / tot1) * ms1 * 1e3 / (n / 16), 2),
+                                 "us_per_launch_bracketed": round(ms * 1e3 / n, 2)}
+                             for c, (ms, n) in prof1.items() if n > 0}
         kvb1.close()
 
         # prefill (config 0: 128-token prompt; a 2048-token prompt in 512-position chunks)
